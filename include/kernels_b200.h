@@ -1,0 +1,168 @@
+/*
+ * kernels_b200 — C ABI of the B200 (sm_100a) streaming-attention library.
+ *
+ * The reference project (alexdremov/kernels) has no native boundary: its Python op
+ * bodies launch Triton kernels directly.  This header declares the entry points that
+ * those op bodies call instead; each one cites the reference interface it replaces
+ * (paths are inside the reference project).
+ *
+ * Conventions
+ *   - every pointer is a raw device pointer unless stated otherwise; the library never
+ *     allocates or frees memory the caller can see and keeps no pointer after returning;
+ *   - tensors are [B, H, T, D]; inputs carry explicit ELEMENT strides, outputs are
+ *     contiguous;
+ *   - all launches go to the `stream` argument (a cudaStream_t passed as void*) on the
+ *     device that is current for the calling thread;
+ *   - return value 0 = success, otherwise a kb_status code; kb_strerror() names it;
+ *   - `status` (optional) points at KB_STATUS_WORDS int32 words the kernels can write
+ *     from the device (pinned host memory is fine).  Word 0 becomes non-zero when a
+ *     bounded wait inside a kernel gave up; the caller reads it after synchronising.
+ */
+#ifndef KERNELS_B200_H_
+#define KERNELS_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define KB_API __attribute__((visibility("default")))
+#else
+#define KB_API
+#endif
+
+#define KB_STATUS_WORDS 4
+
+typedef enum kb_status {
+  KB_OK = 0,
+  KB_ERR_BAD_ARGUMENT = 1,   /* null pointer, negative size, context_size < 1, ...            */
+  KB_ERR_UNSUPPORTED = 2,    /* dtype / head_dim / stride combination no kernel covers       */
+  KB_ERR_LAUNCH = 3,         /* the CUDA runtime refused the launch (see kb_last_cuda_error) */
+  KB_ERR_DEVICE_TIMEOUT = 4, /* a bounded device-side wait gave up (status word set)         */
+  KB_ERR_TOO_LARGE = 5       /* problem exceeds a fixed-size internal buffer                 */
+} kb_status;
+
+typedef enum kb_dtype { KB_F32 = 0, KB_F16 = 1, KB_BF16 = 2 } kb_dtype;
+
+/* flags for the attention entry points */
+#define KB_FLAG_PRESCALE_QK 1u   /* accepted for signature parity; scaling is always done in fp32 */
+#define KB_FLAG_ALLOW_TF32 2u    /* precision="tf32": accepted, fp32 inputs still use IEEE fp32    */
+#define KB_FLAG_FORCE_GENERIC 4u /* skip the tcgen05 path even where it applies (tests)           */
+
+/* which kernel family an attention call resolves to (see kb_sa_select_path) */
+#define KB_PATH_GENERIC 0 /* CUDA-core path: any dtype, head_dim, stride                 */
+#define KB_PATH_SM100 1   /* TMA + tcgen05/TMEM path: f16/bf16, D in {64,128}, dense rows */
+
+typedef struct kb_tensor4 {
+  const void* data;
+  int64_t stride[4]; /* element strides of the b, h, t, d axes */
+} kb_tensor4;
+
+/*
+ * Streaming attention forward.
+ * Replaces the Triton launch in `attention_forward_adapter`
+ * (src/streaming_attention/kernel.py:1273-1337, kernel `_streaming_attn_fwd`, lines 205-430).
+ * Rows t >= len_b of `o` are written as 0 and of `lse` as 0; `lse` holds the base-2
+ * log-sum-exp (kernel.py:407-408) and may be NULL.
+ */
+typedef struct kb_sa_fwd_params {
+  kb_tensor4 q, k, v;
+  void* o;             /* [B,H,T,D] contiguous, same dtype as q */
+  float* lse;          /* [B,H,T] contiguous fp32, or NULL       */
+  const int32_t* lens; /* [B] or NULL (= every length is T)      */
+  int64_t lens_stride;
+  int32_t B, H, T, D;
+  int32_t dtype; /* kb_dtype */
+  int32_t context_size;
+  int32_t back_contexts;
+  float sm_scale;
+  uint32_t flags;
+  int32_t* status; /* KB_STATUS_WORDS words, or NULL */
+} kb_sa_fwd_params;
+
+KB_API int kb_sa_fwd(const kb_sa_fwd_params* p, void* stream);
+
+/*
+ * Streaming attention backward: dQ, dK, dV from (q, k, v, o, lse, do).
+ * Replaces both launches in `attention_backward_adapter`
+ * (src/streaming_attention/kernel.py:1363-1442: `_streaming_attn_bwd_precompute`, lines
+ * 453-514, and `_streaming_attn_bwd`, lines 530-635).  delta = rowsum(o * do) is computed
+ * inside the dQ pass and handed to the dK/dV pass through `delta_ws`.
+ * Rows t >= len_b of dq, dk, dv are written as 0.
+ */
+typedef struct kb_sa_bwd_params {
+  kb_tensor4 q, k, v, o, d_o;
+  const float* lse; /* [B,H,T] contiguous fp32, base 2 */
+  void* dq;         /* [B,H,T,D] contiguous, dtype of q */
+  void* dk;
+  void* dv;
+  float* delta_ws; /* scratch, [B,H,T] fp32, caller-allocated */
+  const int32_t* lens;
+  int64_t lens_stride;
+  int32_t B, H, T, D;
+  int32_t dtype;
+  int32_t context_size;
+  int32_t back_contexts;
+  float sm_scale;
+  uint32_t flags;
+  int32_t* status;
+} kb_sa_bwd_params;
+
+KB_API int kb_sa_bwd(const kb_sa_bwd_params* p, void* stream);
+
+/*
+ * Dense (non-causal) self-attention forward with key padding by `lens`.
+ * Replaces the Triton launch in the op body of `alexdremov_flash_attention::forward`
+ * (src/self_attention/kernel.py:362-414, kernel `_self_attn_fwd`, lines 125-302).
+ * Same parameter block as the streaming forward; context_size/back_contexts are ignored
+ * (the dense schedule is the streaming schedule with a single chunk).
+ */
+KB_API int kb_fa_fwd(const kb_sa_fwd_params* p, void* stream);
+
+/*
+ * Row softmax over the last axis of a [rows, cols] fp32/f16/bf16 matrix.
+ * Replaces `softmax_kernel` and its launch in `softmax()` (src/softmax/kernel.py:27-91).
+ */
+typedef struct kb_softmax_params {
+  const void* x;
+  void* y;
+  int64_t rows, cols;
+  int64_t x_row_stride; /* elements; inner stride is 1 (kernel.py:41) */
+  int64_t y_row_stride;
+  int32_t dtype;
+} kb_softmax_params;
+
+KB_API int kb_softmax_fwd(const kb_softmax_params* p, void* stream);
+
+/*
+ * Host-only: the tile schedule the kernels walk, for one sequence.
+ * fwd_ranges[2*i], fwd_ranges[2*i+1] = first / one-past-last KV tile visited by q tile i
+ * (src/streaming_attention/kernel.py:243-244, 282-291); bwd_ranges likewise the q tiles
+ * visited by KV tile j (kernel.py:1046-1054).  A tile that lies wholly in the padding
+ * gets (0, 0).  Either output pointer may be NULL.  Returns the number of q tiles.
+ */
+KB_API int kb_sa_plan(int32_t T, int32_t seq_len, int32_t context_size, int32_t back_contexts, int32_t tile_q,
+               int32_t tile_k, int32_t* fwd_ranges, int32_t* bwd_ranges);
+
+/*
+ * Host-only: the committed tile table that replaces the reference's per-GPU config
+ * tables and autotuner (src/streaming_attention/kernel.py:17-192, 1133-1267).
+ * Writes the kernel family (KB_PATH_*) and its q/kv tile sizes and pipeline depth for
+ * the forward (`which` = 0), the dQ pass (1) or the dK/dV pass (2).
+ */
+KB_API int kb_sa_tile_config(int32_t dtype, int32_t D, int32_t context_size, uint32_t flags, int32_t unit_inner_stride,
+                      int32_t which, int32_t* path, int32_t* tile_q, int32_t* tile_k, int32_t* stages);
+
+/* number of kernels the library launched since it was loaded (all entry points) */
+KB_API int64_t kb_launch_count(void);
+
+KB_API const char* kb_strerror(int status);
+KB_API const char* kb_last_cuda_error(void);
+KB_API const char* kb_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* KERNELS_B200_H_ */

@@ -1,0 +1,150 @@
+"""CPU: the C-ABI library loads, exports what include/kernels_b200.h declares, validates its
+arguments, and its host planner reproduces the oracle's tile schedule bit for bit."""
+
+import ctypes
+import os
+import re
+
+import pytest
+import torch
+
+from kernels_b200 import _lib
+from oracle import streaming_attention_oracle as SO
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _declared_symbols():
+    text = open(os.path.join(ROOT, "include", "kernels_b200.h")).read()
+    return re.findall(r"KB_API\s+[\w\s\*]+?\b(kb_\w+)\s*\(", text)
+
+
+def test_library_exports_every_declared_symbol():
+    lib = _lib.load()
+    names = _declared_symbols()
+    assert len(names) >= 10 and set(names) == set(_lib.EXPORTS)
+    for n in names:
+        assert getattr(lib, n) is not None
+    assert b"sm_100a" in lib.kb_version()
+
+
+@pytest.mark.parametrize("T", [1, 10, 16, 800])
+@pytest.mark.parametrize("c", [1, 10, 32, 256, 10000])
+@pytest.mark.parametrize("back", [0, 2, 5, 10000])
+@pytest.mark.parametrize("tiles", [(64, 64), (128, 128), (32, 32), (128, 64)])
+def test_plan_is_bit_exact_against_oracle(T, c, back, tiles):
+    tq, tk = tiles
+    for L in sorted({1, 2, 5, c, c + 1, max(c - 1, 1), max(c * back, 1), T + 1, T, max(T // 2, 1), max(T // 4, 1)}):
+        Le = min(L, T)
+        fwd, bwd = _lib.plan(T, min(L, 2**31 - 1), c, back, tq, tk)
+        for i, got in enumerate(fwd):
+            want = SO.fwd_kv_tile_range(i * tq, tq, tk, Le, c, back)
+            assert got == (want if want is not None else (0, 0)), (T, c, back, L, i)
+        for j, got in enumerate(bwd):
+            want = SO.bwd_q_tile_range(j * tk, tq, tk, Le, c, back)
+            assert got == (want if want is not None else (0, 0)), (T, c, back, L, j)
+
+
+def test_plan_handles_extreme_parameters_without_overflow():
+    big = 2**31 - 1
+    fwd, bwd = _lib.plan(1000, big, big, big, 128, 128)
+    assert fwd == [(0, 8)] * 8 and bwd == [(0, 8)] * 8
+    fwd, _ = _lib.plan(1000, 1000, 1, big, 128, 128)
+    assert fwd == [(0, i + 1) for i in range(8)]
+    fwd, _ = _lib.plan(1000, -5, 16, 2, 128, 128)
+    assert fwd == [(0, 0)] * 8
+
+
+def test_argument_validation_without_a_gpu():
+    lib = _lib.load()
+    assert lib.kb_sa_fwd(None, None) == 1
+    p = _lib.SaFwdParams()
+    p.B, p.H, p.T, p.D, p.dtype, p.context_size, p.back_contexts = 1, 1, 8, 48, _lib.KB_F16, 4, 1
+    assert lib.kb_sa_fwd(ctypes.byref(p), None) == 2  # head_dim 48
+    p.D, p.context_size = 64, 0
+    assert lib.kb_sa_fwd(ctypes.byref(p), None) == 1  # context_size < 1
+    p.context_size, p.back_contexts = 4, -1
+    assert lib.kb_sa_fwd(ctypes.byref(p), None) == 1
+    p.back_contexts, p.dtype = 1, 7
+    assert lib.kb_sa_fwd(ctypes.byref(p), None) == 2  # dtype
+    p.dtype = _lib.KB_F16
+    assert lib.kb_sa_fwd(ctypes.byref(p), None) == 1  # null tensors
+    p.T = 0
+    assert lib.kb_sa_fwd(ctypes.byref(p), None) == 0  # empty problem: nothing to do
+    b = _lib.SaBwdParams()
+    b.B, b.H, b.T, b.D, b.dtype, b.context_size = 1, 1, 8, 64, _lib.KB_BF16, 4
+    assert lib.kb_sa_bwd(ctypes.byref(b), None) == 1
+    s = _lib.SoftmaxParams()
+    s.rows, s.cols, s.dtype = 4, 4, _lib.KB_F32
+    assert lib.kb_softmax_fwd(ctypes.byref(s), None) == 1
+    s.rows = 0
+    assert lib.kb_softmax_fwd(ctypes.byref(s), None) == 0
+    assert b"bad argument" in lib.kb_strerror(1)
+    with pytest.raises(RuntimeError, match="unsupported"):
+        _lib.check(2, "x")
+
+
+def test_tile_table():
+    for dt in (torch.float16, torch.bfloat16):
+        for D in (64, 128):
+            cfg = _lib.tile_config(dt, D, 256, which=0)
+            assert cfg["tile_q"] % 16 == 0 and cfg["tile_k"] % 16 == 0 and cfg["stages"] >= 1
+    cfg = _lib.tile_config(torch.float32, 128, 256)
+    assert cfg["path"] == _lib.KB_PATH_GENERIC
+    cfg = _lib.tile_config(torch.float16, 64, 256, flags=_lib.KB_FLAG_FORCE_GENERIC)
+    assert cfg["path"] == _lib.KB_PATH_GENERIC
+
+
+def test_missing_library_fails_loudly(monkeypatch):
+    monkeypatch.setattr(_lib, "_lib", None)
+    monkeypatch.setattr(_lib, "LIB_PATH", "/nonexistent/libkernels_b200.so")
+    with pytest.raises(RuntimeError, match="no fallback"):
+        _lib.load()
+
+
+def test_operators_have_no_cpu_path():
+    from kernels_b200.softmax import softmax
+    from kernels_b200.streaming_attention import streaming_attention  # noqa: F401
+
+    q = torch.randn(1, 1, 8, 16)
+    with pytest.raises((NotImplementedError, RuntimeError)):
+        torch.ops.alexdremov_streaming_attention.forward(q, q, q, None, 4, 1, 0.25, False, False, False, "ieee")
+    with pytest.raises(RuntimeError):
+        softmax(q)
+
+
+def test_fake_implementations_trace_on_meta():
+    """pt2 boundary: shapes/dtypes of the fake (meta) kernels, as the reference's fakes give them."""
+    import kernels_b200.self_attention  # noqa: F401
+    import kernels_b200.streaming_attention  # noqa: F401
+    from torch._subclasses.fake_tensor import FakeTensorMode
+
+    with FakeTensorMode():
+        q = torch.empty(3, 4, 50, 64, dtype=torch.float16, device="cuda").transpose(1, 2).transpose(1, 2)
+        lens = torch.empty(3, dtype=torch.int32, device="cuda")
+        o, lse = torch.ops.alexdremov_streaming_attention.forward(q, q, q, lens, 8, 2, 0.125, False, True, False, "ieee")
+        assert o.shape == q.shape and o.dtype == q.dtype and o.is_contiguous()
+        assert lse.shape == (3, 4, 50) and lse.dtype == torch.float32
+        o2, lse2 = torch.ops.alexdremov_streaming_attention.forward(q, q, q, None, 8, 2, 0.125, False, False, False, "ieee")
+        assert lse2.numel() == 0
+        dq, dk, dv = torch.ops.alexdremov_streaming_attention.backward(
+            q, q, q, lens, o, lse, o, 8, 2, 0.125, False, False, "ieee")
+        assert dq.shape == dk.shape == dv.shape == q.shape
+        o3 = torch.ops.alexdremov_flash_attention.forward(q, q, q, lens, 0.125, True, False)
+        assert o3.shape == q.shape
+
+
+def test_operator_schemas_keep_reference_argument_order():
+    import kernels_b200.self_attention  # noqa: F401
+    import kernels_b200.streaming_attention  # noqa: F401
+
+    fwd = torch.ops.alexdremov_streaming_attention.forward.default._schema
+    assert [a.name for a in fwd.arguments] == [
+        "q", "k", "v", "lens", "context_size", "back_contexts", "sm_scale", "autotune", "return_lse",
+        "prescale_qk", "precision"]
+    bwd = torch.ops.alexdremov_streaming_attention.backward.default._schema
+    assert [a.name for a in bwd.arguments] == [
+        "q", "k", "v", "lens", "o", "lse", "do", "context_size", "back_contexts", "sm_scale", "autotune",
+        "prescale_qk", "precision"]
+    fa = torch.ops.alexdremov_flash_attention.forward.default._schema
+    assert [a.name for a in fa.arguments] == ["q", "k", "v", "lens", "sm_scale", "autotune", "prescale"]
