@@ -1,0 +1,413 @@
+#!/usr/bin/env python
+"""Benchmark of the streaming-attention hot path (forward + backward) on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload cfg3|cfg2|cfg5] [--impl reference]
+
+One step = one forward + backward of the operator over one batch of synthetic input.
+Prints ONE JSON line on rank 0:
+
+* ``value``     useful (unmasked) TFLOP/s of the whole job, inputs resident in HBM, timed with
+                CUDA events on the launching stream, max over ranks;
+* ``e2e``       the same metric through the public Python API with HOST (pinned) buffers:
+                host->device copies of q, k, v, dO and device->host copies of O, dQ, dK, dV
+                are inside the timed region;
+* ``roofline``  the dominant kernel (dK/dV pass) against the measured bf16 tensor peak;
+* ``cpu_baseline`` the CPU oracle (a port of the reference's torch masked-attention path)
+                timed on this machine's host cores on a bounded sample of the same workload.
+
+``--impl reference`` times that CPU path alone (rank 0 only) and prints the same line shape.
+
+Multi-GPU: launched by ``torch.distributed.run`` with one rank per GPU.  The batch x heads
+slices are sharded over ranks (weak scaling for cfg3/cfg2: every rank gets a full copy of the
+single-GPU workload's size; strong scaling for cfg5); there is no collective on the data path,
+NCCL carries only the timing barrier and the max-reduction of the elapsed time.
+"""
+
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # BASELINE.json configs[2]: the configuration the >= 60 %-of-peak target is quoted on
+    "cfg3": dict(dtype="bf16", B=4, H=32, T=16384, D=128, c=256, back=2, lens=None, qk_scale=1.0, scaling="weak",
+                 desc="bf16 B=4 H=32 T=16384 D=128 context=256 back=2 lens=T (per GPU)"),
+    # configs[1]
+    "cfg2": dict(dtype="f16", B=8, H=16, T=4096, D=64, c=128, back=4, lens=(2048, 4096), qk_scale=64 ** -0.25,
+                 scaling="weak", desc="fp16 B=8 H=16 T=4096 D=64 context=128 back=4 lens~U[2048,4096] (per GPU)"),
+    # configs[4]: fixed total problem, batch x heads split over the GPUs
+    "cfg5": dict(dtype="bf16", B=64, H=32, T=8192, D=128, c=64, back=8, lens=(4096, 8192), qk_scale=1.0,
+                 scaling="strong", desc="bf16 B=64 H=32 T=8192 D=128 context=64 back=8 lens~U[4096,8192] (total)"),
+}
+TORCH_DTYPES = {"bf16": torch.bfloat16, "f16": torch.float16, "f32": torch.float32}
+
+
+def _peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as fh:
+            p = json.load(fh)
+        return dict(tflops=p["bf16_tflops"], tflops_sustained=p.get("bf16_tflops_sustained", p["bf16_tflops"]),
+                    hbm_gbs=p["hbm_gbs"], source="measured")
+    return dict(tflops=1590.0, tflops_sustained=1400.0, hbm_gbs=6650.0, source="fallback")
+
+
+class ClockSampler:
+    """Polls nvidia-smi for SM clock and throttle reasons while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.samples, self._stop, self._thr = index, [], threading.Event(), None
+
+    def _run(self):
+        while not self._stop.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                                      "-i", str(self.index)], capture_output=True, text=True, timeout=5).stdout.strip()
+                if out:
+                    self.samples.append([x.strip() for x in out.split(",")])
+            except Exception:
+                pass
+            self._stop.wait(0.1)
+
+    def __enter__(self):
+        self._thr = threading.Thread(target=self._run, daemon=True)
+        self._thr.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        self._thr.join(timeout=6)
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for s in self.samples:
+            try:
+                sm.append(float(s[0]))
+                mx.append(float(s[1]))
+            except (ValueError, IndexError):
+                continue
+            for n, v in zip(names, s[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return dict(sm_mhz=statistics.median(sm) if sm else None, sm_max_mhz=max(mx) if mx else None,
+                    reasons=sorted(reasons), samples=len(sm))
+
+
+# ------------------------------------------------------------------------------------------
+# workload construction
+# ------------------------------------------------------------------------------------------
+def _global_problem(w, n_gpus):
+    """Global batch and lens for N GPUs (weak: batch grows with N; strong: fixed)."""
+    from kernels_b200 import synthetic as SO
+
+    B = w["B"] * n_gpus if w["scaling"] == "weak" else w["B"]
+    lens = None
+    if w["lens"] is not None:
+        lens = SO.make_lens(B, w["lens"][0], w["lens"][1], seed=0)
+    return B, lens
+
+
+def _useful_pairs_total(w, B, lens, heads):
+    from kernels_b200.sharding import useful_pairs
+
+    T = w["T"]
+    ls = [T] * B if lens is None else [min(int(x), T) for x in lens.tolist()]
+    return heads * sum(useful_pairs(L, w["c"], w["back"]) for L in ls), heads * sum(ls)
+
+
+def _make_local_inputs(w, B, heads, H, dtype, pin):
+    """Host tensors [B, len(heads), T, D] for this rank, one seeded generator per (b, h) slice."""
+    from kernels_b200 import synthetic as SO
+
+    T, D = w["T"], w["D"]
+    shape = (B, len(heads), T, D)
+    host = [torch.empty(shape, dtype=dtype, pin_memory=pin) for _ in range(4)]
+    for b in range(B):
+        for j, h in enumerate(heads):
+            sl = SO.make_slice(b, h, H, T, D, seed=0, qk_scale=w["qk_scale"])
+            for dst, src in zip(host, sl):
+                dst[b, j].copy_(src)
+    return host  # q, k, v, do
+
+
+# ------------------------------------------------------------------------------------------
+# reference arm / CPU baseline: the oracle port on the host cores
+# ------------------------------------------------------------------------------------------
+def _cpu_step(w, b, h, H, lens):
+    """One CPU step = dense masked SDPA forward + backward of ONE (batch, head) slice."""
+    from kernels_b200 import synthetic
+    from oracle import streaming_attention_oracle as SO  # the CPU leg is the one place the oracle is timed
+
+    q, k, v, do = synthetic.make_slice(b, h, H, w["T"], w["D"], seed=0, qk_scale=w["qk_scale"])
+    lens_t = None if lens is None else lens[b:b + 1]
+    t0 = time.perf_counter()
+    SO.oracle_fwd_bwd(q[None, None], k[None, None], v[None, None], do[None, None], w["c"], w["back"], lens_t)
+    return time.perf_counter() - t0
+
+
+def _cpu_baseline(w, steps, warmup, budget_s=25.0):
+    from kernels_b200.sharding import useful_pairs
+
+    torch.set_num_threads(os.cpu_count() or 1)
+    B, lens = _global_problem(w, 1)
+    H, T = w["H"], w["T"]
+    times, flops = [], []
+    t_start = time.perf_counter()
+    for i in range(warmup + steps):
+        b, h = (i // H) % B, i % H
+        dt = _cpu_step(w, b, h, H, lens)
+        if i >= warmup:
+            L = T if lens is None else min(int(lens[b]), T)
+            times.append(dt)
+            flops.append(14.0 * w["D"] * useful_pairs(L, w["c"], w["back"]))
+        if budget_s is not None and time.perf_counter() - t_start > budget_s and len(times) >= 1:
+            break
+    tflops = sum(flops) / sum(times) / 1e12
+    return dict(value=tflops, unit="TFLOP/s", cores=torch.get_num_threads(), kind="port",
+                sample=f"{len(times)} (batch, head) slices of the workload, dense masked SDPA fwd+bwd in fp32, "
+                       f"{statistics.mean(times) * 1e3:.0f} ms per slice"), statistics.mean(times) * 1e3
+
+
+def run_reference(args, w):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    base, ms = _cpu_baseline(w, args.steps, args.warmup, budget_s=None)
+    line = {
+        "impl": "reference", "metric": "streaming-attn fwd+bwd useful TFLOP/s", "value": base["value"],
+        "unit": "TFLOP/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
+        "higher_is_better": True, "scaling": w["scaling"], "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": w["desc"], "step": "one (batch, head) slice per step on the host cores"},
+        "cpu_baseline": base,
+        "e2e": {"value": base["value"], "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+# ------------------------------------------------------------------------------------------
+# own arm
+# ------------------------------------------------------------------------------------------
+def _bwd_params(lib_mod, q, k, v, o, do, lse, dq, dk, dv, delta, lens, w, flags):
+    p = lib_mod.SaBwdParams()
+    p.q, p.k, p.v, p.o, p.d_o = (lib_mod.tensor4(t) for t in (q, k, v, o, do))
+    p.lse, p.dq, p.dk, p.dv, p.delta_ws = lse.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), delta.data_ptr()
+    p.lens = lens.data_ptr() if lens is not None else None
+    p.lens_stride = lens.stride(0) if lens is not None else 0
+    p.B, p.H, p.T, p.D = q.shape
+    p.dtype = lib_mod.dtype_code(q.dtype)
+    p.context_size, p.back_contexts, p.sm_scale = w["c"], w["back"], float(w["D"] ** -0.5)
+    p.flags = flags
+    p.status = lib_mod.status_words().data_ptr()
+    return p
+
+
+def run_own(args, w):
+    import torch.distributed as dist
+
+    from kernels_b200 import _lib
+    from kernels_b200.sharding import partition
+    from kernels_b200.streaming_attention import streaming_attention
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    lib = _lib.load()
+    dtype = TORCH_DTYPES[w["dtype"]]
+    H, T, D = w["H"], w["T"], w["D"]
+
+    B, lens = _global_problem(w, world)
+    shard = partition(B, H, world, None if lens is None else lens.tolist(), T=T, context_size=w["c"],
+                      back_contexts=w["back"])[rank]
+    assert shard.mode == "heads", "bench workloads have H divisible by the GPU count"
+    heads = list(shard.heads)
+    hq, hk, hv, hdo = _make_local_inputs(w, B, heads, H, dtype, pin=True)
+    q, k, v, do = (t.to(dev) for t in (hq, hk, hv, hdo))
+    lens_d = lens.to(dev) if lens is not None else None
+    pairs_local, rows_local = _useful_pairs_total(w, B, lens, len(heads))
+    pairs_total, _ = _useful_pairs_total(w, B, lens, H)
+    flops_total = 14.0 * D * pairs_total
+    scale = float(D ** -0.5)
+
+    # ---- device-resident path through the C ABI, one call per kernel so each can be timed ----
+    o = torch.empty_like(q)
+    lse = torch.empty(q.shape[:3], dtype=torch.float32, device=dev)
+    dq, dk, dv = (torch.empty_like(q) for _ in range(3))
+    delta = torch.empty(q.shape[:3], dtype=torch.float32, device=dev)
+    fp = _lib.SaFwdParams()
+    fp.q, fp.k, fp.v = _lib.tensor4(q), _lib.tensor4(k), _lib.tensor4(v)
+    fp.o, fp.lse = o.data_ptr(), lse.data_ptr()
+    fp.lens = lens_d.data_ptr() if lens_d is not None else None
+    fp.lens_stride = lens_d.stride(0) if lens_d is not None else 0
+    fp.B, fp.H, fp.T, fp.D = q.shape
+    fp.dtype = _lib.dtype_code(dtype)
+    fp.context_size, fp.back_contexts, fp.sm_scale, fp.flags = w["c"], w["back"], scale, 0
+    fp.status = _lib.status_words().data_ptr()
+    bp_dq = _bwd_params(_lib, q, k, v, o, do, lse, dq, dk, dv, delta, lens_d, w, _lib.KB_FLAG_BWD_SKIP_DKDV)
+    bp_dkdv = _bwd_params(_lib, q, k, v, o, do, lse, dq, dk, dv, delta, lens_d, w, _lib.KB_FLAG_BWD_SKIP_DQ)
+    stream = torch.cuda.current_stream(dev)
+
+    def step(events=None):
+        marks = []
+        for fn, prm in ((lib.kb_sa_fwd, fp), (lib.kb_sa_bwd, bp_dq), (lib.kb_sa_bwd, bp_dkdv)):
+            if events is not None:
+                e0 = torch.cuda.Event(enable_timing=True)
+                e0.record(stream)
+            _lib.check(fn(ctypes.byref(prm), stream.cuda_stream), "bench step")
+            if events is not None:
+                e1 = torch.cuda.Event(enable_timing=True)
+                e1.record(stream)
+                marks.append((e0, e1))
+        if events is not None:
+            events.append(marks)
+
+    def barrier():
+        torch.cuda.synchronize(dev)
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    _lib.check_device_status()
+
+    launches0 = _lib.launch_count()
+    per_kernel = []
+    with ClockSampler(local_rank) as clk:
+        barrier()
+        t_begin, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t_begin.record(stream)
+        for _ in range(args.steps):
+            step(per_kernel)
+        t_end.record(stream)
+        barrier()
+    launches = _lib.launch_count() - launches0
+    _lib.check_device_status()
+    elapsed_ms = t_begin.elapsed_time(t_end)
+    t = torch.tensor([elapsed_ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    elapsed_ms = float(t.item())
+    ms_per_step = elapsed_ms / args.steps
+    value = flops_total / (ms_per_step * 1e-3) / 1e12
+    k_ms = [statistics.mean(m[i][0].elapsed_time(m[i][1]) for m in per_kernel) for i in range(3)]
+
+    # ---- end to end through the public API with host buffers ----
+    qd, kd, vd = (torch.empty_like(q).requires_grad_() for _ in range(3))
+    dod = torch.empty_like(q)
+    ho, hdq, hdk, hdv = (torch.empty(q.shape, dtype=dtype, pin_memory=True) for _ in range(4))
+
+    def e2e_step():
+        with torch.no_grad():
+            for dst, src in ((qd, hq), (kd, hk), (vd, hv), (dod, hdo)):
+                dst.copy_(src, non_blocking=True)
+        for t_ in (qd, kd, vd):
+            t_.grad = None
+        out = streaming_attention(qd, kd, vd, lens_d, w["c"], w["back"])
+        out.backward(dod)
+        ho.copy_(out.detach(), non_blocking=True)
+        hdq.copy_(qd.grad, non_blocking=True)
+        hdk.copy_(kd.grad, non_blocking=True)
+        hdv.copy_(vd.grad, non_blocking=True)
+
+    e2e_steps = max(1, min(args.steps, 10))
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record(stream)
+    barrier()
+    te = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(te, op=dist.ReduceOp.MAX)
+    e2e_ms = float(te.item()) / e2e_steps
+    tensor_bytes = q.numel() * q.element_size()
+    _lib.check_device_status()
+
+    if rank == 0:
+        peaks = _peaks()
+        peak = peaks["tflops_sustained"] if ms_per_step * args.steps > 500 else peaks["tflops"]
+        # dominant kernel: the dK/dV pass; its algorithmic work is the 4 matmuls it cannot avoid
+        dkdv_flops = 8.0 * D * pairs_local
+        achieved = dkdv_flops / (k_ms[2] * 1e-3) / 1e12
+        el = q.element_size()
+        line = {
+            "metric": "streaming-attn fwd+bwd useful TFLOP/s", "value": value, "unit": "TFLOP/s",
+            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step,
+            "higher_is_better": True, "scaling": w["scaling"], "vs_baseline": None, "dtype": w["dtype"],
+            "data": "synthetic", "impl": "kernels_b200",
+            "config": {"workload": w["desc"], "name": args.workload, "global_batch": B, "heads_per_gpu": len(heads),
+                       "sharding": f"batch x heads, heads round-robin over {world} GPU(s), no collective",
+                       "l2": "inputs larger than L2 (no flush needed)" if 4 * tensor_bytes > 4 * 126e6 else "L2 not flushed",
+                       "useful_flops_per_step": flops_total},
+            "per_gpu_tflops": value / world,
+            "frac_of_bf16_peak": {"measured_burst": value / world / peaks["tflops"],
+                                  "measured_sustained": value / world / peaks["tflops_sustained"],
+                                  "spec_2250": value / world / 2250.0},
+            "kernel_ms": {"fwd": k_ms[0], "bwd_dq": k_ms[1], "bwd_dkdv": k_ms[2]},
+            "kernel_tflops": {"fwd": 4.0 * D * pairs_local / k_ms[0] / 1e9, "bwd_dq": 2.0 * D * pairs_local / k_ms[1] / 1e9,
+                              "bwd_dkdv": achieved},
+            "roofline": {"kernel": "backward dK/dV pass", "bound": "tensor", "achieved": achieved, "peak": peak,
+                         "unit": "TFLOP/s", "frac": achieved / peak, "peak_source": peaks["source"], "traffic": None,
+                         "hbm_min_bytes_fwd_bwd": 12 * rows_local * D * el + 8 * rows_local,
+                         "hbm_frac_if_min_traffic": (12 * rows_local * D * el + 8 * rows_local) / (ms_per_step * 1e-3) / 1e9
+                         / peaks["hbm_gbs"]},
+            "e2e": {"value": flops_total / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
+                    "h2d_bytes_per_step": 4 * tensor_bytes * world, "d2h_bytes_per_step": 4 * tensor_bytes * world,
+                    "steps": e2e_steps},
+            "gpu_launches": launches,
+            "clocks": clk.summary(),
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"], _ = _cpu_baseline(w, steps=6, warmup=1, budget_s=25.0)
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--workload", default="cfg3", choices=sorted(WORKLOADS))
+    ap.add_argument("--impl", default="own", choices=["own", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    w = WORKLOADS[args.workload]
+    if args.impl == "reference":
+        run_reference(args, w)
+    else:
+        run_own(args, w)
+
+
+if __name__ == "__main__":
+    main()

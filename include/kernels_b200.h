@@ -50,6 +50,10 @@ typedef enum kb_dtype { KB_F32 = 0, KB_F16 = 1, KB_BF16 = 2 } kb_dtype;
 #define KB_FLAG_PRESCALE_QK 1u   /* accepted for signature parity; scaling is always done in fp32 */
 #define KB_FLAG_ALLOW_TF32 2u    /* precision="tf32": accepted, fp32 inputs still use IEEE fp32    */
 #define KB_FLAG_FORCE_GENERIC 4u /* skip the tcgen05 path even where it applies (tests)           */
+/* backward only, for per-kernel timing: run one of the two passes.  The dK/dV pass reads the
+ * delta a previous dQ pass over the same inputs left in delta_ws. */
+#define KB_FLAG_BWD_SKIP_DQ 8u
+#define KB_FLAG_BWD_SKIP_DKDV 16u
 
 /* which kernel family an attention call resolves to (see kb_sa_select_path) */
 #define KB_PATH_GENERIC 0 /* CUDA-core path: any dtype, head_dim, stride                 */

@@ -17,6 +17,7 @@ LIB_PATH = os.path.join(_PKG_DIR, "lib", "libkernels_b200.so")
 KB_STATUS_WORDS = 4
 KB_F32, KB_F16, KB_BF16 = 0, 1, 2
 KB_FLAG_PRESCALE_QK, KB_FLAG_ALLOW_TF32, KB_FLAG_FORCE_GENERIC = 1, 2, 4
+KB_FLAG_BWD_SKIP_DQ, KB_FLAG_BWD_SKIP_DKDV = 8, 16
 KB_PATH_GENERIC, KB_PATH_SM100 = 0, 1
 
 _DTYPES = {torch.float32: KB_F32, torch.float16: KB_F16, torch.bfloat16: KB_BF16}

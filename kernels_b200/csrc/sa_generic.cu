@@ -498,10 +498,14 @@ int launch_bwd(const kb_sa_bwd_params& p, int32_t c, int32_t back, cudaStream_t 
   a.scale_log2 = p.sm_scale * kLog2e;
   a.sm_scale = p.sm_scale;
   dim3 grid_q(kb_cdiv_i32(p.T, BM), p.H, p.B), grid_k(kb_cdiv_i32(p.T, BN), p.H, p.B);
-  kern_dq<<<grid_q, kThreads, smem_dq, s>>>(a);
-  KB_LAUNCH_CHECK("sa_bwd_dq_generic_kernel");
-  kern_dkdv<<<grid_k, kThreads, smem_dkdv, s>>>(a);
-  KB_LAUNCH_CHECK("sa_bwd_dkdv_generic_kernel");
+  if (!(p.flags & KB_FLAG_BWD_SKIP_DQ)) {
+    kern_dq<<<grid_q, kThreads, smem_dq, s>>>(a);
+    KB_LAUNCH_CHECK("sa_bwd_dq_generic_kernel");
+  }
+  if (!(p.flags & KB_FLAG_BWD_SKIP_DKDV)) {
+    kern_dkdv<<<grid_k, kThreads, smem_dkdv, s>>>(a);
+    KB_LAUNCH_CHECK("sa_bwd_dkdv_generic_kernel");
+  }
   return KB_OK;
 }
 

@@ -150,6 +150,12 @@ def attention_backward_adapter(
         do = do.to(q.dtype)
     if o.dtype != q.dtype:
         o = o.to(q.dtype)
+    if lse.numel() == 0 and q.numel() != 0:
+        # The forward was called directly with return_lse=False although a gradient is wanted
+        # (the public wrapper never does that): rebuild the log-sum-exp with one more forward.
+        _, lse = attention_forward_adapter(
+            q.detach(), k.detach(), v.detach(), lens, context_size, back_contexts, sm_scale, autotune, True,
+            prescale_qk, precision)
     if lse.dtype != torch.float32 or not lse.is_contiguous():
         lse = lse.to(torch.float32).contiguous()
     assert o.shape == q.shape and do.shape == q.shape and tuple(lse.shape) == (B, H, T)

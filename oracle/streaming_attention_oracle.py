@@ -215,23 +215,6 @@ def banded_fwd_bwd(q, k, v, do, context_size, back_contexts, seq_len, scale=None
 
 
 # --------------------------------------------------------------------------- #
-# deterministic synthetic inputs shared by tests, smoke and benchmark
+# deterministic synthetic inputs: the recipe lives with the product's benchmark helpers
 # --------------------------------------------------------------------------- #
-def make_lens(B: int, lo: int, hi: int, seed: int = 0) -> torch.Tensor:
-    """int32 ``[B]`` lengths ~ Uniform-int[lo, hi] from a seeded CPU generator."""
-    g = torch.Generator(device="cpu").manual_seed(seed)
-    return torch.randint(lo, hi + 1, (B,), generator=g, dtype=torch.int32)
-
-
-def make_slice(b: int, h: int, H: int, T: int, D: int, seed: int = 0, qk_scale: float = 1.0):
-    """fp32 ``q, k, v, do`` of shape ``[T, D]`` for one (batch, head) slice.
-
-    The generator is seeded with ``seed * 1_000_003 + b * H + h`` so the data of a slice
-    does not depend on how batch x heads is spread over GPUs.
-    """
-    g = torch.Generator(device="cpu").manual_seed(seed * 1_000_003 + b * H + h)
-    q = torch.randn(T, D, generator=g) * qk_scale
-    k = torch.randn(T, D, generator=g) * qk_scale
-    v = torch.randn(T, D, generator=g) * qk_scale
-    do = torch.randn(T, D, generator=g)
-    return q, k, v, do
+from kernels_b200.synthetic import make_lens, make_slice  # noqa: E402,F401
