@@ -77,7 +77,12 @@ int run_fwd(const kb_sa_fwd_params* p, void* stream, bool dense) {
   const int32_t back = dense ? 0 : kb_clamp_back(p->back_contexts, p->T, c);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
 #ifdef KB_HAVE_SM100
-  if (select_fwd_path(*p) == KB_PATH_SM100) return sa_fwd_sm100(*p, c, back, s);
+  if (select_fwd_path(*p) == KB_PATH_SM100) {
+    // KB_ERR_UNSUPPORTED from the tcgen05 launcher means "this layout has no tensor map":
+    // nothing was launched, the generic kernels take over.
+    const int rc = sa_fwd_sm100(*p, c, back, s);
+    if (rc != KB_ERR_UNSUPPORTED) return rc;
+  }
 #endif
   return sa_fwd_generic(*p, c, back, s);
 }
@@ -103,7 +108,10 @@ int kb_sa_bwd(const kb_sa_bwd_params* p, void* stream) {
   const int32_t back = kb_clamp_back(p->back_contexts, p->T, c);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
 #ifdef KB_HAVE_SM100_BWD
-  if (kb::select_bwd_path(*p) == KB_PATH_SM100) return kb::sa_bwd_sm100(*p, c, back, s);
+  if (kb::select_bwd_path(*p) == KB_PATH_SM100) {
+    const int rc = kb::sa_bwd_sm100(*p, c, back, s);
+    if (rc != KB_ERR_UNSUPPORTED) return rc;
+  }
 #endif
   return kb::sa_bwd_generic(*p, c, back, s);
 }

@@ -1,0 +1,55 @@
+// Host helper for the sm_100a kernels: TMA tensor maps over strided [B, H, T, D] tensors.
+// The driver's encoder is looked up at run time, so the library carries no link-time
+// dependency on libcuda and still loads on a machine without a GPU driver.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/kernels_b200.h"
+
+namespace kb {
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+inline EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      p = nullptr;
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  return fn;
+}
+
+// Map over a 16-bit [B, H, T, D] tensor with element strides; a box is [box_rows x 64]
+// elements of one (b, h) (128 bytes per row, SWIZZLE_128B); rows past T read as zeros.
+// Returns false when the layout cannot be described (the caller then uses the generic path).
+inline bool make_tile_map_4d(CUtensorMap* out, const kb_tensor4& t, int B, int H, int T, int D, int box_rows) {
+  EncodeTiledFn enc = encode_tiled_fn();
+  if (!enc) return false;
+  if (t.stride[3] != 1 || reinterpret_cast<uintptr_t>(t.data) % 16) return false;
+  const cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)T, (cuuint64_t)H, (cuuint64_t)B};
+  int64_t st[3] = {t.stride[2], t.stride[1], t.stride[0]};  // t, h, b
+  const int64_t extent[3] = {T, H, B};
+  // a dimension of extent 1 may carry any stride: give it a harmless valid one
+  int64_t fallback = D;
+  for (int i = 0; i < 3; ++i) {
+    if (extent[i] == 1) st[i] = fallback;
+    if (st[i] <= 0 || (st[i] * 2) % 16 || st[i] * 2 >= ((int64_t)1 << 40)) return false;
+    fallback = st[i] * extent[i];
+  }
+  const cuuint64_t strides[3] = {(cuuint64_t)st[0] * 2, (cuuint64_t)st[1] * 2, (cuuint64_t)st[2] * 2};
+  const cuuint32_t box[4] = {64, (cuuint32_t)box_rows, 1, 1};
+  const cuuint32_t elem[4] = {1, 1, 1, 1};
+  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(t.data), dims, strides, box, elem,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+}  // namespace kb
