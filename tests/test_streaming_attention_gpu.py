@@ -17,6 +17,14 @@ from oracle import streaming_attention_oracle as SO
 pytestmark = pytest.mark.gpu
 
 
+@pytest.fixture(autouse=True)
+def _fresh_dynamo_cache():
+    # the public function is torch.compile'd; like the reference's tests, start each test with an
+    # empty Dynamo cache so that the sweep over shapes and dtypes never hits the recompile limit
+    torch._dynamo.reset()
+    yield
+
+
 def _api():
     from kernels_b200.streaming_attention import streaming_attention
 
