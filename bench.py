@@ -30,7 +30,6 @@ import ctypes
 import json
 import os
 import statistics
-import subprocess
 import sys
 import threading
 import time
@@ -51,6 +50,9 @@ WORKLOADS = {
     # configs[4]: fixed total problem, batch x heads split over the GPUs
     "cfg5": dict(dtype="bf16", B=64, H=32, T=8192, D=128, c=64, back=8, lens=(4096, 8192), qk_scale=1.0,
                  scaling="strong", desc="bf16 B=64 H=32 T=8192 D=128 context=64 back=8 lens~U[4096,8192] (total)"),
+    # small stand-in for cfg3 (same tiles and schedule, 1/4 of the slices) for ncu captures
+    "prof": dict(dtype="bf16", B=2, H=16, T=16384, D=128, c=256, back=2, lens=None, qk_scale=1.0, scaling="weak",
+                 desc="bf16 B=2 H=16 T=16384 D=128 context=256 back=2 lens=T (profiling case)"),
 }
 TORCH_DTYPES = {"bf16": torch.bfloat16, "f16": torch.float16, "f32": torch.float32}
 
@@ -66,28 +68,39 @@ def _peaks():
 
 
 class ClockSampler:
-    """Polls nvidia-smi for SM clock and throttle reasons while the timed region runs."""
+    """Samples SM clock and throttle reasons through NVML (read-only) while the timed region runs."""
 
-    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
-
-    def __init__(self, index: int):
-        self.index, self.samples, self._stop, self._thr = index, [], threading.Event(), None
+    def __init__(self, index: int, period_s: float = 0.01):
+        self.index, self.period, self.samples, self._stop, self._thr = index, period_s, [], threading.Event(), None
 
     def _run(self):
-        while not self._stop.is_set():
-            try:
-                out = subprocess.run(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                                      "-i", str(self.index)], capture_output=True, text=True, timeout=5).stdout.strip()
-                if out:
-                    self.samples.append([x.strip() for x in out.split(",")])
-            except Exception:
-                pass
-            self._stop.wait(0.1)
+        try:
+            import pynvml as nv
+
+            nv.nvmlInit()
+            # NVML indexes physical devices; honour CUDA_VISIBLE_DEVICES when it lists indices
+            vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+            idx = self.index
+            if vis and all(x.strip().isdigit() for x in vis.split(",")):
+                idx = int(vis.split(",")[self.index])
+            hnd = nv.nvmlDeviceGetHandleByIndex(idx)
+            mx = nv.nvmlDeviceGetMaxClockInfo(hnd, nv.NVML_CLOCK_SM)
+            bits = {"hw_slowdown": nv.nvmlClocksThrottleReasonHwSlowdown,
+                    "hw_thermal_slowdown": nv.nvmlClocksThrottleReasonHwThermalSlowdown,
+                    "sw_thermal_slowdown": nv.nvmlClocksThrottleReasonSwThermalSlowdown,
+                    "sw_power_cap": nv.nvmlClocksThrottleReasonSwPowerCap}
+            while not self._stop.is_set():
+                sm = nv.nvmlDeviceGetClockInfo(hnd, nv.NVML_CLOCK_SM)
+                rs = nv.nvmlDeviceGetCurrentClocksThrottleReasons(hnd)
+                self.samples.append((float(sm), float(mx), [n for n, b in bits.items() if rs & b]))
+                self._stop.wait(self.period)
+        except Exception as e:  # no NVML: report that no clock record exists
+            self.samples.append((None, None, [f"nvml unavailable: {type(e).__name__}"]))
 
     def __enter__(self):
         self._thr = threading.Thread(target=self._run, daemon=True)
         self._thr.start()
+        time.sleep(0.05)
         return self
 
     def __exit__(self, *exc):
@@ -95,19 +108,11 @@ class ClockSampler:
         self._thr.join(timeout=6)
 
     def summary(self):
-        sm, mx, reasons = [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for s in self.samples:
-            try:
-                sm.append(float(s[0]))
-                mx.append(float(s[1]))
-            except (ValueError, IndexError):
-                continue
-            for n, v in zip(names, s[2:6]):
-                if v.lower().startswith("active"):
-                    reasons.add(n)
-        return dict(sm_mhz=statistics.median(sm) if sm else None, sm_max_mhz=max(mx) if mx else None,
-                    reasons=sorted(reasons), samples=len(sm))
+        sm = [s[0] for s in self.samples if s[0] is not None]
+        mx = [s[1] for s in self.samples if s[1] is not None]
+        reasons = sorted({r for s in self.samples for r in s[2]})
+        return dict(sm_mhz=statistics.median(sm) if sm else None, sm_min_mhz=min(sm) if sm else None,
+                    sm_max_mhz=max(mx) if mx else None, reasons=reasons, samples=len(sm))
 
 
 # ------------------------------------------------------------------------------------------
@@ -334,8 +339,8 @@ def run_own(args, w):
         hdk.copy_(kd.grad, non_blocking=True)
         hdv.copy_(vd.grad, non_blocking=True)
 
-    e2e_steps = max(1, min(args.steps, 10))
-    for _ in range(3):
+    e2e_steps = 0 if args.no_e2e else max(1, min(args.steps, 10))
+    for _ in range(3 if e2e_steps else 0):
         e2e_step()
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -347,7 +352,7 @@ def run_own(args, w):
     te = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(te, op=dist.ReduceOp.MAX)
-    e2e_ms = float(te.item()) / e2e_steps
+    e2e_ms = float(te.item()) / max(e2e_steps, 1)
     tensor_bytes = q.numel() * q.element_size()
     _lib.check_device_status()
 
@@ -379,7 +384,7 @@ def run_own(args, w):
                          "hbm_min_bytes_fwd_bwd": 12 * rows_local * D * el + 8 * rows_local,
                          "hbm_frac_if_min_traffic": (12 * rows_local * D * el + 8 * rows_local) / (ms_per_step * 1e-3) / 1e9
                          / peaks["hbm_gbs"]},
-            "e2e": {"value": flops_total / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
+            "e2e": None if not e2e_steps else {"value": flops_total / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": 4 * tensor_bytes * world, "d2h_bytes_per_step": 4 * tensor_bytes * world,
                     "steps": e2e_steps},
             "gpu_launches": launches,
@@ -401,6 +406,7 @@ def main():
     ap.add_argument("--workload", default="cfg3", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="own", choices=["own", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     args = ap.parse_args()
     w = WORKLOADS[args.workload]
     if args.impl == "reference":

@@ -17,8 +17,10 @@
 // The MMA warp issues Z(t+1) before the accumulation of tile t, so the tensor pipe works on
 // one tile while the four compute warps turn the other tile's scores into P / dS.
 //
-// Roles: warps 0-3 compute (thread r owns row r = TMEM lane r), warp 4 TMA producer (plus the
-// per-column lse/delta staging of the dK/dV pass), warp 5 MMA issuer and TMEM owner.
+// Roles: warps 0-7 compute (two warpgroups; a thread owns row (warp % 4) * 32 + lane = its TMEM
+// lane, and warpgroup g the columns [32 g, 32 g + 32) of every 64-column tile), warp 8 TMA
+// producer (plus the per-column lse/delta staging of the dK/dV pass), warp 9 MMA issuer and
+// TMEM owner.
 // TMEM columns: Z1[2] at 0/64, Z2[2] at 128/192, accumulator 1 at 256, accumulator 2 at 384.
 //
 // Reference semantics: src/streaming_attention/kernel.py:453-514 (delta), 639-773 and
@@ -36,8 +38,10 @@ using namespace sm100;
 
 constexpr int kBX = 128;  // stationary rows per CTA
 constexpr int kBY = 64;   // streamed rows per tile
-constexpr int kStages = 3;
-constexpr int kThreads = 192;
+constexpr int kStages = 4;
+constexpr int kComputeWarps = 8;
+constexpr int kThreads = (kComputeWarps + 2) * 32;
+constexpr int kProducerWarp = kComputeWarps, kMmaWarp = kComputeWarps + 1;
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kColZ1 = 0, kColZ2 = 128, kColAcc1 = 256, kColAcc2 = 384;
 
@@ -63,8 +67,8 @@ struct alignas(1024) BwdSmem {
   uint8_t a2[kBX * D * 2];
   uint8_t y1[kStages][kBY * D * 2];
   uint8_t y2[kStages][kBY * D * 2];
-  float lse_s[kStages][kBY];
-  float delta_s[kStages][kBY];
+  alignas(16) float lse_s[kStages][kBY];
+  alignas(16) float delta_s[kStages][kBY];
   uint64_t x_full, y_full[kStages], y_empty[kStages], z_ready[2], p_ready[2], z_free[2], acc_done;
   uint32_t tmem_base;
   int abort_flag;
@@ -117,14 +121,14 @@ sa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_a1, const __grid_cons
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&sm.z_ready[i], 1);
-      mbar_init(&sm.p_ready[i], kBX);
+      mbar_init(&sm.p_ready[i], kComputeWarps * 32);
       mbar_init(&sm.z_free[i], 1);
     }
     mbar_init(&sm.acc_done, 1);
     sm.abort_flag = 0;
     fence_mbar_init();
   }
-  if (warp == 5) tmem_alloc(&sm.tmem_base, kTmemCols);
+  if (warp == kMmaWarp) tmem_alloc(&sm.tmem_base, kTmemCols);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -134,7 +138,7 @@ sa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_a1, const __grid_cons
   constexpr uint32_t kXPanelBytes = kBX * 128, kYPanelBytes = kBY * 128;
   constexpr uint32_t kXBytes = kBX * D * 2, kYBytes = kBY * D * 2;
 
-  if (warp == 4) {
+  if (warp == kProducerWarp) {
     // ------------------------------ producer ------------------------------
     if (lane == 0) {
       prefetch_tensormap(&tm_a1);
@@ -174,7 +178,7 @@ sa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_a1, const __grid_cons
         }
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == kMmaWarp) {
     // ------------------------------ MMA issuer ------------------------------
     if (lane == 0) {
       constexpr uint32_t idesc_z = make_idesc(BF16, kBX, kBY, false, false);
@@ -209,11 +213,13 @@ sa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_a1, const __grid_cons
 #pragma unroll
           for (int kk = 0; kk < kBY / 16; ++kk) {
             const bool acc = u > 0 || kk > 0;
+            // 16 reduction rows = 8 packed columns; rows [32 g, 32 g + 32) sit at columns 32 g ..
+            const uint32_t ko = (kk / 2) * 32 + (kk % 2) * 8;
             if (kDQ) {
-              mma_ts(tmem + kColAcc1, ds_addr + kk * 8, desc_mnmajor(y1_addr + kk * 2048, kYPanelBytes), idesc_acc, acc);
+              mma_ts(tmem + kColAcc1, ds_addr + ko, desc_mnmajor(y1_addr + kk * 2048, kYPanelBytes), idesc_acc, acc);
             } else {
-              mma_ts(tmem + kColAcc1, p_addr + kk * 8, desc_mnmajor(y2_addr + kk * 2048, kYPanelBytes), idesc_acc, acc);
-              mma_ts(tmem + kColAcc2, ds_addr + kk * 8, desc_mnmajor(y1_addr + kk * 2048, kYPanelBytes), idesc_acc, acc);
+              mma_ts(tmem + kColAcc1, p_addr + ko, desc_mnmajor(y2_addr + kk * 2048, kYPanelBytes), idesc_acc, acc);
+              mma_ts(tmem + kColAcc2, ds_addr + ko, desc_mnmajor(y1_addr + kk * 2048, kYPanelBytes), idesc_acc, acc);
             }
           }
           mma_commit(&sm.y_empty[s]);
@@ -224,7 +230,8 @@ sa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_a1, const __grid_cons
     }
   } else {
     // ------------------------------ compute warps + epilogue ------------------------------
-    const int row = threadIdx.x;
+    const int row = (warp & 3) * 32 + lane;
+    const int half = warp >> 2;  // which 32 columns of each 64-column tile this warpgroup owns
     const int xi = x0 + row;
     // live columns of this row form one interval [lo, hi)
     int lo = 0, hi = 0;
@@ -240,7 +247,7 @@ sa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_a1, const __grid_cons
         hi = h64 < len ? (int)h64 : len;
       }
     }
-    const uint32_t t_lane = tmem + ((uint32_t)(warp * 32) << 16);
+    const uint32_t t_lane = tmem + ((uint32_t)((warp & 3) * 32) << 16);
     const float scale = a.scale_log2;
 
     float lse_r = 0.f, delta_r = 0.f;
@@ -248,6 +255,7 @@ sa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_a1, const __grid_cons
       if (xi < len) {
         const uint4* orow = reinterpret_cast<const uint4*>(a.o + b * a.o_sb + h * a.o_sh + (int64_t)xi * a.o_st);
         const uint4* grow = reinterpret_cast<const uint4*>(a.d_o + b * a.do_sb + h * a.do_sh + (int64_t)xi * a.do_st);
+        float part[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll 4
         for (int i = 0; i < D * 2 / 16; ++i) {
           const uint4 ov = __ldg(orow + i), gv = __ldg(grow + i);
@@ -267,52 +275,67 @@ sa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_a1, const __grid_cons
               g0 = __low2float(gh);
               g1 = __high2float(gh);
             }
-            delta_r = fmaf(o0, g0, delta_r);
-            delta_r = fmaf(o1, g1, delta_r);
+            part[w] = fmaf(o0, g0, part[w]);
+            part[w] = fmaf(o1, g1, part[w]);
           }
         }
+        delta_r = (part[0] + part[1]) + (part[2] + part[3]);
         lse_r = a.lse[bh * T + xi];
       }
-      if (xi < T) a.delta[bh * T + xi] = delta_r;
+      if (half == 0 && xi < T) a.delta[bh * T + xi] = delta_r;
     }
 
     bool ok = true;
     for (int t = 0; t < n_tiles; ++t) {
       const int s = t % kStages, buf = t & 1;
-      const int y0 = (yr.begin + t) * kBY;
+      const int y0 = (yr.begin + t) * kBY + half * 32;  // first column this thread handles
       ok = __all_sync(0xffffffffu, mbar_wait(&sm.z_ready[buf], (t / 2) & 1, ctx, kWZReady));
       if (!ok) break;
       tc_fence_after();
-      const bool warp_full = __all_sync(0xffffffffu, lo <= y0 && y0 + kBY <= hi);
+      const bool warp_full = __all_sync(0xffffffffu, lo <= y0 && y0 + 32 <= hi);
+      const uint32_t t_z1 = t_lane + kColZ1 + buf * kBY, t_z2 = t_lane + kColZ2 + buf * kBY;
+      uint32_t z1[32], z2[32];
+      tmem_ld32(t_z1 + half * 32, z1);
+      tmem_ld32(t_z2 + half * 32, z2);
+      float lse_c[32], delta_c[32];
+      if (!kDQ) {
 #pragma unroll
-      for (int cc = 0; cc < kBY / 32; ++cc) {
-        uint32_t z1[32], z2[32];
-        tmem_ld32(t_lane + kColZ1 + buf * kBY + cc * 32, z1);
-        tmem_ld32(t_lane + kColZ2 + buf * kBY + cc * 32, z2);
-        tmem_wait_ld();
-        uint32_t pk_p[16], pk_ds[16];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          float p[2], ds[2];
-#pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            const int cidx = cc * 32 + 2 * i + e;
-            const float lse_c = kDQ ? lse_r : sm.lse_s[s][cidx];
-            const float delta_c = kDQ ? delta_r : sm.delta_s[s][cidx];
-            float pv = ex2_approx(fmaf(__uint_as_float(z1[2 * i + e]), scale, -lse_c));
-            if (!warp_full) {
-              const int col = y0 + cidx;
-              pv = (col >= lo && col < hi) ? pv : 0.f;
-            }
-            p[e] = pv;
-            ds[e] = pv * (__uint_as_float(z2[2 * i + e]) - delta_c);
-          }
-          pk_p[i] = pack16x2<BF16>(p[0], p[1]);
-          pk_ds[i] = pack16x2<BF16>(ds[0], ds[1]);
+        for (int i = 0; i < 8; ++i) {
+          const float4 lv = *reinterpret_cast<const float4*>(&sm.lse_s[s][half * 32 + 4 * i]);
+          const float4 dv = *reinterpret_cast<const float4*>(&sm.delta_s[s][half * 32 + 4 * i]);
+          lse_c[4 * i] = lv.x, lse_c[4 * i + 1] = lv.y, lse_c[4 * i + 2] = lv.z, lse_c[4 * i + 3] = lv.w;
+          delta_c[4 * i] = dv.x, delta_c[4 * i + 1] = dv.y, delta_c[4 * i + 2] = dv.z, delta_c[4 * i + 3] = dv.w;
         }
-        if (!kDQ) tmem_st16(t_lane + kColZ1 + buf * kBY + cc * 16, pk_p);
-        tmem_st16(t_lane + kColZ2 + buf * kBY + cc * 16, pk_ds);
       }
+      tmem_wait_ld();
+      uint32_t pk_p[16], pk_ds[16];
+      if (warp_full) {
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          const float p0 = ex2_approx(fmaf(__uint_as_float(z1[i]), scale, -(kDQ ? lse_r : lse_c[i])));
+          const float p1 = ex2_approx(fmaf(__uint_as_float(z1[i + 1]), scale, -(kDQ ? lse_r : lse_c[i + 1])));
+          const float d0 = p0 * (__uint_as_float(z2[i]) - (kDQ ? delta_r : delta_c[i]));
+          const float d1 = p1 * (__uint_as_float(z2[i + 1]) - (kDQ ? delta_r : delta_c[i + 1]));
+          if (!kDQ) pk_p[i / 2] = pack16x2<BF16>(p0, p1);
+          pk_ds[i / 2] = pack16x2<BF16>(d0, d1);
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          float p0 = ex2_approx(fmaf(__uint_as_float(z1[i]), scale, -(kDQ ? lse_r : lse_c[i])));
+          float p1 = ex2_approx(fmaf(__uint_as_float(z1[i + 1]), scale, -(kDQ ? lse_r : lse_c[i + 1])));
+          p0 = (y0 + i >= lo && y0 + i < hi) ? p0 : 0.f;
+          p1 = (y0 + i + 1 >= lo && y0 + i + 1 < hi) ? p1 : 0.f;
+          const float d0 = p0 * (__uint_as_float(z2[i]) - (kDQ ? delta_r : delta_c[i]));
+          const float d1 = p1 * (__uint_as_float(z2[i + 1]) - (kDQ ? delta_r : delta_c[i + 1]));
+          if (!kDQ) pk_p[i / 2] = pack16x2<BF16>(p0, p1);
+          pk_ds[i / 2] = pack16x2<BF16>(d0, d1);
+        }
+      }
+      // each warpgroup overlays its 16-bit values on the fp32 columns it has just consumed itself
+      // (columns [32 g, 32 g + 16) of the buffer), so the two warpgroups never touch each other's data
+      if (!kDQ) tmem_st16(t_z1 + half * 32, pk_p);
+      tmem_st16(t_z2 + half * 32, pk_ds);
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(&sm.p_ready[buf]);
@@ -328,12 +351,13 @@ sa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_a1, const __grid_cons
         const float mul = (kDQ || which == 1) ? a.sm_scale : 1.f;
         uint16_t* out = which == 0 ? out1 : out2;
 #pragma unroll
-        for (int cc = 0; cc < D / 32; ++cc) {
+        for (int cc = 0; cc < D / 64; ++cc) {
+          const int c32 = half * (D / 64) + cc;  // this warpgroup's share of the D columns
           uint32_t r[32];
-          tmem_ld32(t_lane + col0 + cc * 32, r);
+          tmem_ld32(t_lane + col0 + c32 * 32, r);
           tmem_wait_ld();
           if (xi < T) {
-            uint4* dst = reinterpret_cast<uint4*>(out + (int64_t)xi * D + cc * 32);
+            uint4* dst = reinterpret_cast<uint4*>(out + (int64_t)xi * D + c32 * 32);
 #pragma unroll
             for (int g = 0; g < 4; ++g) {
               uint4 w;
@@ -351,7 +375,7 @@ sa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_a1, const __grid_cons
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 5) {
+  if (warp == kMmaWarp) {
     if (sm.abort_flag) __nanosleep(1000000);  // let copies still in flight land before the CTA goes away
     tmem_dealloc(tmem, kTmemCols);
   }

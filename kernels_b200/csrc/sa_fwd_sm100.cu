@@ -1,16 +1,18 @@
 // Streaming-attention forward for sm_100a: TMA -> shared memory -> tcgen05.mma -> TMEM.
 //
 // One CTA owns one tile of 128 query rows of one (batch, head) and walks only the live KV
-// tiles of the streaming schedule (schedule.h).  Six warps, three roles:
-//   warps 0-3  softmax: thread t owns query row t (= TMEM lane t).  Reads S from TMEM, keeps the
-//              running max / sum, writes P (16-bit) back over S, rescales O when the max
-//              moved by more than 2^8, and writes O / LSE at the end;
-//   warp 4     TMA producer (one lane): Q once, then K and V tiles;
+// tiles (64 keys each) of the streaming schedule (schedule.h).  Six warps, three roles:
+//   warps 0-3  softmax: thread t owns query row t (= TMEM lane t).  Reads a 128 x 64 block of
+//              S from TMEM into registers, keeps the running max / sum, writes P (16-bit) back
+//              over S, rescales O when the max moved by more than 2^8, writes O / LSE at the end;
+//   warp 4     TMA producer (one lane): Q once, then a ring of K/V tiles;
 //   warp 5     MMA issuer (one lane): S = Q K^T (A, B from shared memory), O += P V
 //              (A = P from TMEM, B = V from shared memory, MN-major); owns the TMEM allocation.
-// TMEM columns: [0,128) S (fp32), overlaid by P in [0,64); [128,128+D) O (fp32).  256 columns
-// per CTA and one K and one V buffer keep two CTAs resident per SM: while one CTA is in its
-// softmax the other one's MMAs use the tensor pipe.
+// S is double buffered in TMEM and the MMA warp issues S(t+1) before P(t) V(t), so the tensor
+// pipe works on one KV tile while the softmax warps are busy with the other.
+// TMEM columns: [0,64) and [64,128) the two S buffers (fp32; P overlays the first 32 columns of
+// each); [128,128+D) O (fp32).  256 columns and ~100 KB of shared memory per CTA keep two CTAs
+// resident per SM.
 //
 // Masking uses the fact that the live keys of a query row form one interval
 // [max(0, i/c - back) * c, min((i/c + 1) * c, len)), which is the element form of the mask
@@ -29,10 +31,11 @@ namespace {
 
 using namespace sm100;
 
-constexpr int kBM = 128, kBN = 128;
+constexpr int kBM = 128, kBN = 64;
+constexpr int kStages = 2;
 constexpr int kThreads = 192;
 constexpr uint32_t kTmemCols = 256;
-constexpr uint32_t kColS = 0, kColP = 0, kColO = 128;
+constexpr uint32_t kColS = 0, kColO = 128;
 constexpr float kRescaleThreshold = 8.f;  // log2 units
 
 struct FwdArgs {
@@ -48,14 +51,63 @@ struct FwdArgs {
 template <int D>
 struct alignas(1024) FwdSmem {
   uint8_t q[kBM * D * 2];
-  uint8_t k[kBN * D * 2];
-  uint8_t v[kBN * D * 2];
-  uint64_t q_full, k_full, v_full, k_empty, v_empty, s_ready, p_ready, pv_done;
+  uint8_t k[kStages][kBN * D * 2];
+  uint8_t v[kStages][kBN * D * 2];
+  uint64_t q_full, k_full[kStages], k_empty[kStages], v_full[kStages], v_empty[kStages], s_ready[2], p_ready[2], pv_done, o_done;
   uint32_t tmem_base;
   int abort_flag;
 };
 
 enum WaitSite { kWaitQ = 1, kWaitKEmpty, kWaitVEmpty, kWaitKFull, kWaitVFull, kWaitSReady, kWaitPReady, kWaitPvDone, kWaitEpilogue };
+
+// One 128 x 64 block of scores for the thread's row: online softmax update, P into TMEM.
+// kMasked = false is the fast path for blocks in which every element of the warp's rows is live.
+template <bool BF16, bool kMasked>
+__device__ __forceinline__ void softmax_block(uint32_t t_s, float scale, int k0, int lo, int hi, float& m_used, float& l,
+                                              bool& need_rescale, float& alpha) {
+  uint32_t s[kBN];
+  tmem_ld32(t_s, reinterpret_cast<uint32_t(&)[32]>(s[0]));
+  tmem_ld32(t_s + 32, reinterpret_cast<uint32_t(&)[32]>(s[32]));
+  tmem_wait_ld();
+  if (kMasked) {
+#pragma unroll
+    for (int i = 0; i < kBN; ++i) {
+      const int col = k0 + i;
+      s[i] = (col >= lo && col < hi) ? s[i] : 0xff800000u;  // -inf
+    }
+  }
+  float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+  for (int i = 0; i < kBN; i += 4) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) mx[e] = fmaxf(mx[e], __uint_as_float(s[i + e]));
+  }
+  const float m_new = fmaxf(m_used, fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * scale);
+  // lazy rescale: keep the old reference maximum unless the new one is > 2^8 larger
+  need_rescale = m_new > m_used + kRescaleThreshold;
+  alpha = 1.f;
+  if (need_rescale) {
+    alpha = ex2_approx(m_used - m_new);
+    m_used = m_new;
+    l *= alpha;
+  }
+  const float m_safe = (m_used == -INFINITY) ? 0.f : m_used;
+  float sum[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+  for (int cc = 0; cc < kBN / 32; ++cc) {
+    uint32_t pk[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const float p0 = ex2_approx(fmaf(__uint_as_float(s[cc * 32 + 2 * i]), scale, -m_safe));
+      const float p1 = ex2_approx(fmaf(__uint_as_float(s[cc * 32 + 2 * i + 1]), scale, -m_safe));
+      sum[(2 * i) & 3] += p0;
+      sum[(2 * i + 1) & 3] += p1;
+      pk[i] = pack16x2<BF16>(p0, p1);
+    }
+    tmem_st16(t_s + cc * 16, pk);
+  }
+  l += (sum[0] + sum[1]) + (sum[2] + sum[3]);
+}
 
 template <int D, bool BF16>
 __global__ void __launch_bounds__(kThreads, 2)
@@ -87,13 +139,18 @@ sa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
 
   if (threadIdx.x == 0) {
     mbar_init(&sm.q_full, 1);
-    mbar_init(&sm.k_full, 1);
-    mbar_init(&sm.v_full, 1);
-    mbar_init(&sm.k_empty, 1);
-    mbar_init(&sm.v_empty, 1);
-    mbar_init(&sm.s_ready, 1);
-    mbar_init(&sm.p_ready, kBM);
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&sm.k_full[s], 1);
+      mbar_init(&sm.k_empty[s], 1);
+      mbar_init(&sm.v_full[s], 1);
+      mbar_init(&sm.v_empty[s], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&sm.s_ready[i], 1);
+      mbar_init(&sm.p_ready[i], kBM);
+    }
     mbar_init(&sm.pv_done, 1);
+    mbar_init(&sm.o_done, 1);
     sm.abort_flag = 0;
     fence_mbar_init();
   }
@@ -103,7 +160,7 @@ sa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   tc_fence_after();
   const uint32_t tmem = sm.tmem_base;
   const WaitCtx ctx{&sm.abort_flag, a.status};
-  constexpr uint32_t kTileBytes = kBN * D * 2, kPanelBytes = kBN * 128;
+  constexpr uint32_t kQPanelBytes = kBM * 128, kKvPanelBytes = kBN * 128, kKvBytes = kBN * D * 2;
   constexpr int kPanels = D / 64;
 
   if (warp == 4) {
@@ -114,17 +171,19 @@ sa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       prefetch_tensormap(&tm_v);
       mbar_expect_tx(&sm.q_full, kBM * D * 2);
 #pragma unroll
-      for (int p = 0; p < kPanels; ++p) tma_load_4d(sm.q + p * kPanelBytes, &tm_q, &sm.q_full, p * 64, q0, h, b);
-      for (int j = 0; j < n_tiles; ++j) {
-        const int k0 = (kr.begin + j) * kBN;
-        if (j > 0 && !mbar_wait(&sm.k_empty, (j - 1) & 1, ctx, kWaitKEmpty)) break;
-        mbar_expect_tx(&sm.k_full, kTileBytes);
+      for (int p = 0; p < kPanels; ++p) tma_load_4d(sm.q + p * kQPanelBytes, &tm_q, &sm.q_full, p * 64, q0, h, b);
+      for (int t = 0; t < n_tiles; ++t) {
+        const int s = t % kStages;
+        const int k0 = (kr.begin + t) * kBN;
+        // K is free again as soon as S(t - kStages) is done, V only after P V: separate rings
+        if (t >= kStages && !mbar_wait(&sm.k_empty[s], ((t / kStages) - 1) & 1, ctx, kWaitKEmpty)) break;
+        mbar_expect_tx(&sm.k_full[s], kKvBytes);
 #pragma unroll
-        for (int p = 0; p < kPanels; ++p) tma_load_4d(sm.k + p * kPanelBytes, &tm_k, &sm.k_full, p * 64, k0, h, b);
-        if (j > 0 && !mbar_wait(&sm.v_empty, (j - 1) & 1, ctx, kWaitVEmpty)) break;
-        mbar_expect_tx(&sm.v_full, kTileBytes);
+        for (int p = 0; p < kPanels; ++p) tma_load_4d(sm.k[s] + p * kKvPanelBytes, &tm_k, &sm.k_full[s], p * 64, k0, h, b);
+        if (t >= kStages && !mbar_wait(&sm.v_empty[s], ((t / kStages) - 1) & 1, ctx, kWaitVEmpty)) break;
+        mbar_expect_tx(&sm.v_full[s], kKvBytes);
 #pragma unroll
-        for (int p = 0; p < kPanels; ++p) tma_load_4d(sm.v + p * kPanelBytes, &tm_v, &sm.v_full, p * 64, k0, h, b);
+        for (int p = 0; p < kPanels; ++p) tma_load_4d(sm.v[s] + p * kKvPanelBytes, &tm_v, &sm.v_full[s], p * 64, k0, h, b);
       }
     }
   } else if (warp == 5) {
@@ -132,30 +191,39 @@ sa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     if (lane == 0) {
       constexpr uint32_t idesc_qk = make_idesc(BF16, kBM, kBN, false, false);
       constexpr uint32_t idesc_pv = make_idesc(BF16, kBM, D, false, true);
-      const uint32_t q_addr = smem_u32(sm.q), k_addr = smem_u32(sm.k), v_addr = smem_u32(sm.v);
+      const uint32_t q_addr = smem_u32(sm.q);
       bool ok = mbar_wait(&sm.q_full, 0, ctx, kWaitQ);
-      for (int j = 0; ok && j < n_tiles; ++j) {
-        // S/P columns are reused: the previous P V must have drained them
-        if (j > 0 && !mbar_wait(&sm.pv_done, (j - 1) & 1, ctx, kWaitPvDone)) break;
-        if (!mbar_wait(&sm.k_full, j & 1, ctx, kWaitKFull)) break;
-        tc_fence_after();
+      for (int t = 0; ok && t <= n_tiles; ++t) {
+        if (t < n_tiles) {
+          // S(t) = Q K_t^T.  Its TMEM buffer was last read by P(t-2) V(t-2), issued earlier by
+          // this thread: MMAs execute in issue order, so no wait is needed for the reuse.
+          const int s = t % kStages, buf = t & 1;
+          if (!mbar_wait(&sm.k_full[s], (t / kStages) & 1, ctx, kWaitKFull)) break;
+          tc_fence_after();
+          const uint32_t k_addr = smem_u32(sm.k[s]);
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = (kk / 4) * kPanelBytes + (kk % 4) * 32;
-          mma_ss(tmem + kColS, desc_kmajor(q_addr + off), desc_kmajor(k_addr + off), idesc_qk, kk > 0);
+          for (int kk = 0; kk < D / 16; ++kk) {
+            const uint32_t qo = (kk / 4) * kQPanelBytes + (kk % 4) * 32, ko = (kk / 4) * kKvPanelBytes + (kk % 4) * 32;
+            mma_ss(tmem + kColS + buf * kBN, desc_kmajor(q_addr + qo), desc_kmajor(k_addr + ko), idesc_qk, kk > 0);
+          }
+          mma_commit(&sm.k_empty[s]);
+          mma_commit(&sm.s_ready[buf]);
         }
-        mma_commit(&sm.k_empty);
-        mma_commit(&sm.s_ready);
-        if (!mbar_wait(&sm.p_ready, j & 1, ctx, kWaitPReady)) break;
-        if (!mbar_wait(&sm.v_full, j & 1, ctx, kWaitVFull)) break;
-        tc_fence_after();
+        if (t >= 1) {
+          const int u = t - 1, s = u % kStages, buf = u & 1;
+          if (!mbar_wait(&sm.p_ready[buf], (u / 2) & 1, ctx, kWaitPReady)) break;
+          if (!mbar_wait(&sm.v_full[s], (u / kStages) & 1, ctx, kWaitVFull)) break;
+          tc_fence_after();
+          const uint32_t v_addr = smem_u32(sm.v[s]);
 #pragma unroll
-        for (int kk = 0; kk < kBN / 16; ++kk) {
-          mma_ts(tmem + kColO, tmem + kColP + kk * 8, desc_mnmajor(v_addr + kk * 16 * 128, kPanelBytes), idesc_pv,
-                 j > 0 || kk > 0);
+          for (int kk = 0; kk < kBN / 16; ++kk) {
+            mma_ts(tmem + kColO, tmem + kColS + buf * kBN + kk * 8, desc_mnmajor(v_addr + kk * 2048, kKvPanelBytes),
+                   idesc_pv, u > 0 || kk > 0);
+          }
+          mma_commit(&sm.v_empty[s]);
+          mma_commit(&sm.pv_done);
+          if (u == n_tiles - 1) mma_commit(&sm.o_done);
         }
-        mma_commit(&sm.v_empty);
-        mma_commit(&sm.pv_done);
       }
     }
   } else {
@@ -174,41 +242,24 @@ sa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     float m_used = -INFINITY, l = 0.f;
     bool ok = true;
 
-    for (int j = 0; j < n_tiles; ++j) {
-      const int k0 = (kr.begin + j) * kBN;
-      ok = __all_sync(0xffffffffu, mbar_wait(&sm.s_ready, j & 1, ctx, kWaitSReady));
+    for (int t = 0; t < n_tiles; ++t) {
+      const int buf = t & 1;
+      const int k0 = (kr.begin + t) * kBN;
+      ok = __all_sync(0xffffffffu, mbar_wait(&sm.s_ready[buf], (t / 2) & 1, ctx, kWaitSReady));
       if (!ok) break;
       tc_fence_after();
       const bool warp_full = __all_sync(0xffffffffu, lo <= k0 && k0 + kBN <= hi);
-
-      // pass 1: row maximum of the raw scores
-      float mx = -INFINITY;
-#pragma unroll
-      for (int cc = 0; cc < kBN / 32; ++cc) {
-        uint32_t r[32];
-        tmem_ld32(t_lane + kColS + cc * 32, r);
-        tmem_wait_ld();
-        if (warp_full) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const int col = k0 + cc * 32 + i;
-            mx = fmaxf(mx, (col >= lo && col < hi) ? __uint_as_float(r[i]) : -INFINITY);
-          }
-        }
-      }
-      const float m_new = fmaxf(m_used, mx * scale);
-      // lazy rescale: keep the old reference maximum unless the new one is > 2^8 larger
-      const bool need = m_new > m_used + kRescaleThreshold;
-      float alpha = 1.f;
-      if (need) {
-        alpha = ex2_approx(m_used - m_new);
-        m_used = m_new;
-        l *= alpha;
-      }
-      if (j > 0 && __any_sync(0xffffffffu, need)) {
+      bool need;
+      float alpha;
+      if (warp_full)
+        softmax_block<BF16, false>(t_lane + kColS + buf * kBN, scale, k0, lo, hi, m_used, l, need, alpha);
+      else
+        softmax_block<BF16, true>(t_lane + kColS + buf * kBN, scale, k0, lo, hi, m_used, l, need, alpha);
+      if (t > 0 && __any_sync(0xffffffffu, need)) {
+        // O must not be touched while P(t-1) V(t-1) is still accumulating into it
+        ok = __all_sync(0xffffffffu, mbar_wait(&sm.pv_done, (t - 1) & 1, ctx, kWaitPvDone));
+        if (!ok) break;
+        tc_fence_after();
 #pragma unroll
         for (int cc = 0; cc < D / 32; ++cc) {
           uint32_t r[32];
@@ -219,35 +270,14 @@ sa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
           tmem_st32(t_lane + kColO + cc * 32, r);
         }
       }
-      const float m_safe = (m_used == -INFINITY) ? 0.f : m_used;
-
-      // pass 2: P = 2^(S * scale - m), row sum, 16-bit P back into TMEM over S
-#pragma unroll
-      for (int cc = 0; cc < kBN / 32; ++cc) {
-        uint32_t r[32];
-        tmem_ld32(t_lane + kColS + cc * 32, r);
-        tmem_wait_ld();
-        uint32_t pk[16];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          float p0 = ex2_approx(fmaf(__uint_as_float(r[2 * i]), scale, -m_safe));
-          float p1 = ex2_approx(fmaf(__uint_as_float(r[2 * i + 1]), scale, -m_safe));
-          if (!warp_full) {
-            const int col = k0 + cc * 32 + 2 * i;
-            p0 = (col >= lo && col < hi) ? p0 : 0.f;
-            p1 = (col + 1 >= lo && col + 1 < hi) ? p1 : 0.f;
-          }
-          l += p0 + p1;
-          pk[i] = pack16x2<BF16>(p0, p1);
-        }
-        tmem_st16(t_lane + kColP + cc * 16, pk);
-      }
       tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(&sm.p_ready);
+      mbar_arrive(&sm.p_ready[buf]);
     }
 
-    if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&sm.pv_done, (n_tiles - 1) & 1, ctx, kWaitEpilogue));
+    // A parity wait on pv_done could be two phases behind here (only P(n-3) V(n-3) is known to be
+    // complete), which a parity bit cannot tell apart: the last accumulation has its own barrier.
+    if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&sm.o_done, 0, ctx, kWaitEpilogue));
     if (ok) {
       tc_fence_after();
       const bool valid = qi < len;

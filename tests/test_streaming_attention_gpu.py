@@ -164,6 +164,18 @@ def test_every_head_dim_and_dtype(dtype, D):
     _run_case(2, 2, 130, D, 128, 1, dtype, "tricky", True)
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16], ids=str)
+@pytest.mark.parametrize("D", [64, 128])
+def test_rows_whose_last_tile_is_the_only_live_one(dtype, D):
+    """Shapes in which only some rows of a q tile still have live keys in the last KV tile, and
+    others start with fully masked tiles: the accumulator must be complete before it is read and
+    rescaling from an all-masked prefix must be exact."""
+    for (B, H, T, c, back) in [(1, 1, 512, 32, 7), (1, 1, 1024, 96, 2), (2, 2, 700, 48, 3), (1, 2, 704, 48, 3),
+                               (1, 1, 2048, 256, 2), (1, 1, 1000, 64, 8)]:
+        for seed in (0, 1, 2):
+            _run_case(B, H, T, D, c, back, dtype, "none" if B == 1 else "tricky", False, seed=seed)
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.float16], ids=str)
 def test_opcheck_like_reference(dtype):
     _run_case(2, 2, 16, 64, 10, 5, dtype, "tricky", True, check_ops=True, via="api")
