@@ -66,7 +66,8 @@ def build(force: bool = False, verbose: bool = False) -> str:
         + [os.path.join(INC_DIR, f) for f in os.listdir(INC_DIR) if f.endswith(".h")]
     )
     defines = [FEATURE_DEFINES[s] for s in srcs if s in FEATURE_DEFINES]
-    flags = NVCC_FLAGS + defines + ["-I", INC_DIR]
+    extra = os.environ.get("KB_NVCC_EXTRA", "").split()  # e.g. -DKB_TRACE for the clock-trace build
+    flags = NVCC_FLAGS + defines + extra + ["-I", INC_DIR]
 
     def compile_one(src: str) -> tuple[str, bool, str]:
         src_path = os.path.join(SRC_DIR, src)

@@ -1,27 +1,33 @@
 // Streaming-attention backward for sm_100a: one kernel template, two passes.
 //
 //   dQ pass    (kDQ = true):  a CTA keeps 128 query rows (Q, dO) in shared memory and streams
-//                             64-row K/V tiles over the forward schedule.  It also produces
+//                             128-row K/V tiles over the forward schedule.  It also produces
 //                             delta = rowsum(O * dO) for its rows and leaves it in the
 //                             workspace for the other pass.
-//   dK/dV pass (kDQ = false): a CTA keeps 128 key rows (K, V) and streams 64-row Q/dO tiles
+//   dK/dV pass (kDQ = false): a CTA keeps 128 key rows (K, V) and streams 128-row Q/dO tiles
 //                             over the transposed schedule.
 // Both passes have the same shape.  With X the stationary operands (A1, A2) and Y_t the
 // streamed ones (B1, B2):
-//   Z1 = A1 * B1^T   (scores, 128 x 64)          Z2 = A2 * B2^T   (dP, 128 x 64)
-//   P  = 2^(Z1 * scale - lse[q])                 dS = P * (Z2 - delta[q])      (masked -> 0)
+//   S  = A1 * B1^T   (scores, 128 x 128)         dP = A2 * B2^T   (128 x 128)
+//   P  = 2^(S * scale - lse[q])                  dS = P * (dP - delta[q])      (masked -> 0)
 //   dQ pass:    dQ += dS * K_t                   dK/dV pass: dV += P * dO_t,  dK += dS * Q_t
-// Z1/Z2 live in TMEM, double buffered; P and dS are written back over them as 16-bit values
-// and feed the accumulating MMAs as the A operand straight from TMEM; the streamed tile in
-// shared memory is read K-major by the first two MMAs and MN-major by the accumulating ones.
-// The MMA warp issues Z(t+1) before the accumulation of tile t, so the tensor pipe works on
-// one tile while the four compute warps turn the other tile's scores into P / dS.
+// S and dP live in TMEM; P and dS are written back over them as 16-bit values and feed the
+// accumulating MMAs as the A operand straight from TMEM; the streamed tile in shared memory is
+// read K-major by the first two MMAs and MN-major by the accumulating ones.
+//
+// The tensor pipe and the compute warps overlap by splitting each tile into two phases:
+//   dK/dV pass MMA order:  S(0) dP(0) | dV(t) S(t+1) dK(t) dP(t+1) | ...
+//       while the compute warps turn S(t+1) into P(t+1) the pipe runs dK(t), dP(t+1);
+//       while they turn dP(t+1) into dS(t+1) it runs dV(t+1), S(t+2).
+//   dQ pass MMA order:     S(0) dP(0) S(1) | dQ(t) dP(t+1) S(t+2) | ...   (S double buffered)
+// MMAs execute in issue order, so a buffer that a later MMA overwrites needs no wait on the
+// earlier MMA that reads it; waits exist only where the compute warps or TMA are involved.
 //
 // Roles: warps 0-7 compute (two warpgroups; a thread owns row (warp % 4) * 32 + lane = its TMEM
-// lane, and warpgroup g the columns [32 g, 32 g + 32) of every 64-column tile), warp 8 TMA
-// producer (plus the per-column lse/delta staging of the dK/dV pass), warp 9 MMA issuer and
-// TMEM owner.
-// TMEM columns: Z1[2] at 0/64, Z2[2] at 128/192, accumulator 1 at 256, accumulator 2 at 384.
+// lane, and warpgroup g the columns [64 g, 64 g + 64) of every tile), warp 8 TMA producer (plus
+// the per-column lse/delta staging of the dK/dV pass), warp 9 MMA issuer and TMEM owner.
+// TMEM columns: S at 0 (second S buffer of the dQ pass at 384), dP at 128, accumulator 1 at
+// 256, accumulator 2 (dK) at 384.
 //
 // Reference semantics: src/streaming_attention/kernel.py:453-514 (delta), 639-773 and
 // 941-1023 (dQ), 777-937 and 1027-1129 (dK/dV).  No atomics: results are bitwise repeatable.
@@ -32,18 +38,32 @@
 #include "sm100_host.h"
 
 namespace kb {
+#ifdef KB_TRACE
+// Debug build only (-DKB_TRACE): clock64 stamps of one CTA's pipeline events, read back by
+// kb_debug_trace().  [role: 0 producer, 1 MMA, 2 compute warp 0][tile][slot]
+__device__ long long g_trace[3][64][8];
+#define KB_TR(role, t, slot)                                      \
+  do {                                                            \
+    if (trace_cta && (t) < 64) g_trace[role][t][slot] = clock64(); \
+  } while (0)
+#else
+#define KB_TR(role, t, slot) \
+  do {                       \
+  } while (0)
+#endif
 namespace {
 
 using namespace sm100;
 
 constexpr int kBX = 128;  // stationary rows per CTA
-constexpr int kBY = 64;   // streamed rows per tile
-constexpr int kStages = 4;
+constexpr int kBY = 128;  // streamed rows per tile
+constexpr int kStagesB1 = 3, kStagesB2 = 2;
 constexpr int kComputeWarps = 8;
+constexpr int kComputeThreads = kComputeWarps * 32;
 constexpr int kThreads = (kComputeWarps + 2) * 32;
 constexpr int kProducerWarp = kComputeWarps, kMmaWarp = kComputeWarps + 1;
 constexpr uint32_t kTmemCols = 512;
-constexpr uint32_t kColZ1 = 0, kColZ2 = 128, kColAcc1 = 256, kColAcc2 = 384;
+constexpr uint32_t kColS = 0, kColS1 = 384, kColDP = 128, kColAcc1 = 256, kColAcc2 = 384;
 
 struct BwdArgs {
   // dQ pass: o / d_o rows for delta (element strides of b, h, t; unit inner stride)
@@ -61,28 +81,33 @@ struct BwdArgs {
   int32_t* status;
 };
 
+// Shared memory of one CTA.  At D = 128 this is exactly the 227 KB a CTA may have, which is why
+// the base of dynamic shared memory itself must be 1024-byte aligned (checked at run time)
+// instead of being rounded up inside a larger allocation.
 template <int D>
 struct alignas(1024) BwdSmem {
   uint8_t a1[kBX * D * 2];
   uint8_t a2[kBX * D * 2];
-  uint8_t y1[kStages][kBY * D * 2];
-  uint8_t y2[kStages][kBY * D * 2];
-  alignas(16) float lse_s[kStages][kBY];
-  alignas(16) float delta_s[kStages][kBY];
-  uint64_t x_full, y_full[kStages], y_empty[kStages], z_ready[2], p_ready[2], z_free[2], acc_done;
+  uint8_t b1[kStagesB1][kBY * D * 2];
+  uint8_t b2[kStagesB2][kBY * D * 2];
+  alignas(16) float lse_s[2][kBY];
+  alignas(16) float delta_s[2][kBY];
+  uint64_t x_full, b1_full[kStagesB1], b1_empty[kStagesB1], b2_full[kStagesB2], b2_empty[kStagesB2];
+  uint64_t s_ready[2], dp_ready, p_ready, ds_ready[2], stats_full[2], acc_done;
   uint32_t tmem_base;
   int abort_flag;
 };
 
-enum WaitSite { kWX = 21, kWYEmpty, kWYFull, kWZFree, kWZReady, kWPReady, kWAccDone };
+enum WaitSite { kWX = 21, kWB1Empty, kWB2Empty, kWStats, kWStatsFull, kWB1Full, kWB2Full, kWSReady, kWDpReady, kWPReady, kWDsReady, kWAccDone };
+constexpr int kErrSmemAlign = 41;
 
-template <int D, bool BF16, bool kDQ, bool kWaitZFree>
+template <int D, bool BF16, bool kDQ>
 __global__ void __launch_bounds__(kThreads, 1)
 sa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_a1, const __grid_constant__ CUtensorMap tm_a2,
                     const __grid_constant__ CUtensorMap tm_b1, const __grid_constant__ CUtensorMap tm_b2,
                     const BwdArgs a) {
-  extern __shared__ uint8_t smem_raw[];
-  BwdSmem<D>& sm = *reinterpret_cast<BwdSmem<D>*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  BwdSmem<D>& sm = *reinterpret_cast<BwdSmem<D>*>(smem_raw);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int b = blockIdx.z, h = blockIdx.y, x0 = blockIdx.x * kBX;
@@ -91,6 +116,15 @@ sa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_a1, const __grid_cons
   const int64_t bh = (int64_t)b * a.H + h;
   uint16_t* out1 = static_cast<uint16_t*>(a.out1) + bh * T * D;
   uint16_t* out2 = kDQ ? nullptr : static_cast<uint16_t*>(a.out2) + bh * T * D;
+
+  if (smem_u32(smem_raw) & 1023u) {
+    // swizzled operand tiles need a 1024-byte aligned base: report instead of computing garbage
+    if (threadIdx.x == 0 && a.status) {
+      atomicExch(a.status, KB_ERR_DEVICE_TIMEOUT);
+      atomicExch(a.status + 1, kErrSmemAlign);
+    }
+    return;
+  }
 
   // streamed tiles [begin, end) in units of kBY rows
   const KbTileRange yr = kDQ ? kb_fwd_kv_range(x0, kBX, kBY, len, a.c, a.back) : kb_bwd_q_range(x0, kBY, kBX, len, a.c, a.back);
@@ -112,18 +146,27 @@ sa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_a1, const __grid_cons
     return;
   }
   const int n_tiles = yr.end - yr.begin;
+#ifdef KB_TRACE
+  const bool trace_cta = blockIdx.x == 60 && blockIdx.y == 0 && blockIdx.z == 0 && (kDQ == (KB_TRACE != 0));
+#endif
 
   if (threadIdx.x == 0) {
     mbar_init(&sm.x_full, 1);
-    for (int s = 0; s < kStages; ++s) {
-      mbar_init(&sm.y_full[s], 1);
-      mbar_init(&sm.y_empty[s], 1);
+    for (int s = 0; s < kStagesB1; ++s) {
+      mbar_init(&sm.b1_full[s], 1);
+      mbar_init(&sm.b1_empty[s], 1);
+    }
+    for (int s = 0; s < kStagesB2; ++s) {
+      mbar_init(&sm.b2_full[s], 1);
+      mbar_init(&sm.b2_empty[s], 1);
     }
     for (int i = 0; i < 2; ++i) {
-      mbar_init(&sm.z_ready[i], 1);
-      mbar_init(&sm.p_ready[i], kComputeWarps * 32);
-      mbar_init(&sm.z_free[i], 1);
+      mbar_init(&sm.s_ready[i], 1);
+      mbar_init(&sm.ds_ready[i], kComputeThreads);
+      mbar_init(&sm.stats_full[i], 32);
     }
+    mbar_init(&sm.dp_ready, 1);
+    mbar_init(&sm.p_ready, kComputeThreads);
     mbar_init(&sm.acc_done, 1);
     sm.abort_flag = 0;
     fence_mbar_init();
@@ -135,8 +178,8 @@ sa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_a1, const __grid_cons
   const uint32_t tmem = sm.tmem_base;
   const WaitCtx ctx{&sm.abort_flag, a.status};
   constexpr int kPanels = D / 64;
-  constexpr uint32_t kXPanelBytes = kBX * 128, kYPanelBytes = kBY * 128;
-  constexpr uint32_t kXBytes = kBX * D * 2, kYBytes = kBY * D * 2;
+  constexpr uint32_t kPanelBytes = 128 * 128;  // 128 rows x 128 bytes, both operand kinds
+  constexpr uint32_t kTileBytes = 128 * D * 2;
 
   if (warp == kProducerWarp) {
     // ------------------------------ producer ------------------------------
@@ -145,37 +188,49 @@ sa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_a1, const __grid_cons
       prefetch_tensormap(&tm_a2);
       prefetch_tensormap(&tm_b1);
       prefetch_tensormap(&tm_b2);
-      mbar_expect_tx(&sm.x_full, 2 * kXBytes);
+      mbar_expect_tx(&sm.x_full, 2 * kTileBytes);
 #pragma unroll
       for (int p = 0; p < kPanels; ++p) {
-        tma_load_4d(sm.a1 + p * kXPanelBytes, &tm_a1, &sm.x_full, p * 64, x0, h, b);
-        tma_load_4d(sm.a2 + p * kXPanelBytes, &tm_a2, &sm.x_full, p * 64, x0, h, b);
+        tma_load_4d(sm.a1 + p * kPanelBytes, &tm_a1, &sm.x_full, p * 64, x0, h, b);
+        tma_load_4d(sm.a2 + p * kPanelBytes, &tm_a2, &sm.x_full, p * 64, x0, h, b);
       }
     }
     for (int t = 0; t < n_tiles; ++t) {
-      const int s = t % kStages;
+      const int s1 = t % kStagesB1, s2 = t % kStagesB2;
       const int y0 = (yr.begin + t) * kBY;
       bool ok = true;
-      if (t >= kStages) ok = mbar_wait(&sm.y_empty[s], ((t / kStages) - 1) & 1, ctx, kWYEmpty);
-      if (!__all_sync(0xffffffffu, ok)) break;
+      if (lane == 0) {
+        KB_TR(0, t, 0);
+        if (t >= kStagesB1) ok = mbar_wait(&sm.b1_empty[s1], ((t / kStagesB1) - 1) & 1, ctx, kWB1Empty);
+        if (ok) {
+          mbar_expect_tx(&sm.b1_full[s1], kTileBytes);
+#pragma unroll
+          for (int p = 0; p < kPanels; ++p) tma_load_4d(sm.b1[s1] + p * kPanelBytes, &tm_b1, &sm.b1_full[s1], p * 64, y0, h, b);
+          KB_TR(0, t, 1);
+          if (t >= kStagesB2) ok = mbar_wait(&sm.b2_empty[s2], ((t / kStagesB2) - 1) & 1, ctx, kWB2Empty);
+          KB_TR(0, t, 2);
+        }
+        if (ok) {
+          mbar_expect_tx(&sm.b2_full[s2], kTileBytes);
+#pragma unroll
+          for (int p = 0; p < kPanels; ++p) tma_load_4d(sm.b2[s2] + p * kPanelBytes, &tm_b2, &sm.b2_full[s2], p * 64, y0, h, b);
+        }
+      }
       if (!kDQ) {
-        // per-column statistics of the streamed query rows
+        // per-column statistics (lse, delta) of the streamed query rows, two slots deep: slot t & 1
+        // was last read while dS(t-2) was formed
+        if (ok && t >= 2) ok = mbar_wait(&sm.ds_ready[t & 1], ((t / 2) - 1) & 1, ctx, kWStats);
+        if (!__all_sync(0xffffffffu, ok)) break;
 #pragma unroll
         for (int i = 0; i < kBY / 32; ++i) {
           const int r = y0 + lane + 32 * i;
           const bool valid = r < len;
-          sm.lse_s[s][lane + 32 * i] = valid ? a.lse[bh * T + r] : 0.f;
-          sm.delta_s[s][lane + 32 * i] = valid ? a.delta[bh * T + r] : 0.f;
+          sm.lse_s[t & 1][lane + 32 * i] = valid ? a.lse[bh * T + r] : 0.f;
+          sm.delta_s[t & 1][lane + 32 * i] = valid ? a.delta[bh * T + r] : 0.f;
         }
-        __syncwarp();
-      }
-      if (lane == 0) {
-        mbar_expect_tx(&sm.y_full[s], 2 * kYBytes);
-#pragma unroll
-        for (int p = 0; p < kPanels; ++p) {
-          tma_load_4d(sm.y1[s] + p * kYPanelBytes, &tm_b1, &sm.y_full[s], p * 64, y0, h, b);
-          tma_load_4d(sm.y2[s] + p * kYPanelBytes, &tm_b2, &sm.y_full[s], p * 64, y0, h, b);
-        }
+        mbar_arrive(&sm.stats_full[t & 1]);
+      } else if (!__all_sync(0xffffffffu, ok)) {
+        break;
       }
     }
   } else if (warp == kMmaWarp) {
@@ -184,54 +239,95 @@ sa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_a1, const __grid_cons
       constexpr uint32_t idesc_z = make_idesc(BF16, kBX, kBY, false, false);
       constexpr uint32_t idesc_acc = make_idesc(BF16, kBX, D, false, true);
       const uint32_t a1_addr = smem_u32(sm.a1), a2_addr = smem_u32(sm.a2);
-      bool ok = mbar_wait(&sm.x_full, 0, ctx, kWX);
-      for (int t = 0; ok && t <= n_tiles; ++t) {
-        if (t < n_tiles) {
-          const int s = t % kStages, buf = t & 1;
-          if (!mbar_wait(&sm.y_full[s], (t / kStages) & 1, ctx, kWYFull)) break;
-          if (kWaitZFree && t >= 2 && !mbar_wait(&sm.z_free[buf], ((t / 2) - 1) & 1, ctx, kWZFree)) break;
-          tc_fence_after();
-          const uint32_t y1_addr = smem_u32(sm.y1[s]), y2_addr = smem_u32(sm.y2[s]);
+
+      // S(t) = A1 * B1_t^T into S buffer `sbuf`
+      auto issue_s = [&](int t, int sbuf) -> bool {
+        const int s1 = t % kStagesB1;
+        KB_TR(1, t, 0);
+        if (!mbar_wait(&sm.b1_full[s1], (t / kStagesB1) & 1, ctx, kWB1Full)) return false;
+        KB_TR(1, t, 1);
+        tc_fence_after();
+        const uint32_t b_addr = smem_u32(sm.b1[s1]);
+        const uint32_t d_col = tmem + (sbuf ? kColS1 : kColS);
 #pragma unroll
-          for (int kk = 0; kk < D / 16; ++kk) {
-            const uint32_t xo = (kk / 4) * kXPanelBytes + (kk % 4) * 32, yo = (kk / 4) * kYPanelBytes + (kk % 4) * 32;
-            mma_ss(tmem + kColZ1 + buf * kBY, desc_kmajor(a1_addr + xo), desc_kmajor(y1_addr + yo), idesc_z, kk > 0);
-          }
-#pragma unroll
-          for (int kk = 0; kk < D / 16; ++kk) {
-            const uint32_t xo = (kk / 4) * kXPanelBytes + (kk % 4) * 32, yo = (kk / 4) * kYPanelBytes + (kk % 4) * 32;
-            mma_ss(tmem + kColZ2 + buf * kBY, desc_kmajor(a2_addr + xo), desc_kmajor(y2_addr + yo), idesc_z, kk > 0);
-          }
-          mma_commit(&sm.z_ready[buf]);
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = (kk / 4) * kPanelBytes + (kk % 4) * 32;
+          mma_ss(d_col, desc_kmajor(a1_addr + off), desc_kmajor(b_addr + off), idesc_z, kk > 0);
         }
-        if (t >= 1) {
-          const int u = t - 1, s = u % kStages, buf = u & 1;
-          if (!mbar_wait(&sm.p_ready[buf], (u / 2) & 1, ctx, kWPReady)) break;
-          tc_fence_after();
-          const uint32_t y1_addr = smem_u32(sm.y1[s]), y2_addr = smem_u32(sm.y2[s]);
-          const uint32_t p_addr = tmem + kColZ1 + buf * kBY, ds_addr = tmem + kColZ2 + buf * kBY;
+        mma_commit(&sm.s_ready[sbuf]);
+        KB_TR(1, t, 2);
+        return true;
+      };
+      // dP(t) = A2 * B2_t^T
+      auto issue_dp = [&](int t) -> bool {
+        const int s2 = t % kStagesB2;
+        if (!mbar_wait(&sm.b2_full[s2], (t / kStagesB2) & 1, ctx, kWB2Full)) return false;
+        KB_TR(1, t, 3);
+        tc_fence_after();
+        const uint32_t b_addr = smem_u32(sm.b2[s2]);
 #pragma unroll
-          for (int kk = 0; kk < kBY / 16; ++kk) {
-            const bool acc = u > 0 || kk > 0;
-            // 16 reduction rows = 8 packed columns; rows [32 g, 32 g + 32) sit at columns 32 g ..
-            const uint32_t ko = (kk / 2) * 32 + (kk % 2) * 8;
-            if (kDQ) {
-              mma_ts(tmem + kColAcc1, ds_addr + ko, desc_mnmajor(y1_addr + kk * 2048, kYPanelBytes), idesc_acc, acc);
-            } else {
-              mma_ts(tmem + kColAcc1, p_addr + ko, desc_mnmajor(y2_addr + kk * 2048, kYPanelBytes), idesc_acc, acc);
-              mma_ts(tmem + kColAcc2, ds_addr + ko, desc_mnmajor(y1_addr + kk * 2048, kYPanelBytes), idesc_acc, acc);
-            }
-          }
-          mma_commit(&sm.y_empty[s]);
-          mma_commit(&sm.z_free[buf]);
-          if (u == n_tiles - 1) mma_commit(&sm.acc_done);
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = (kk / 4) * kPanelBytes + (kk % 4) * 32;
+          mma_ss(tmem + kColDP, desc_kmajor(a2_addr + off), desc_kmajor(b_addr + off), idesc_z, kk > 0);
+        }
+        if (kDQ) mma_commit(&sm.b2_empty[s2]);  // V_t has no other reader in the dQ pass
+        mma_commit(&sm.dp_ready);
+        KB_TR(1, t, 4);
+        return true;
+      };
+      // acc += A(tmem, 16-bit at `a_col`) * B(smem tile at b_addr, MN-major)
+      auto issue_acc = [&](uint32_t acc_col, uint32_t a_col, uint32_t b_addr, bool first_tile) {
+#pragma unroll
+        for (int kk = 0; kk < kBY / 16; ++kk) {
+          // 16 reduction rows = 8 packed columns; rows [64 g, 64 g + 64) sit at columns 64 g ..
+          const uint32_t ko = (kk / 4) * 64 + (kk % 4) * 8;
+          mma_ts(tmem + acc_col, tmem + a_col + ko, desc_mnmajor(b_addr + kk * 2048, kPanelBytes), idesc_acc,
+                 !first_tile || kk > 0);
+        }
+      };
+
+      bool ok = mbar_wait(&sm.x_full, 0, ctx, kWX);
+      if (kDQ) {
+        ok = ok && issue_s(0, 0) && issue_dp(0);
+        if (ok && n_tiles > 1) ok = issue_s(1, 1);
+        for (int t = 0; ok && t < n_tiles; ++t) {
+          const int s1 = t % kStagesB1;
+          KB_TR(1, t, 5);
+          if (!mbar_wait(&sm.ds_ready[t & 1], (t / 2) & 1, ctx, kWDsReady)) break;
+          KB_TR(1, t, 6);
+          tc_fence_after();
+          issue_acc(kColAcc1, kColDP, smem_u32(sm.b1[s1]), t == 0);  // dQ += dS * K_t
+          mma_commit(&sm.b1_empty[s1]);
+          KB_TR(1, t, 7);
+          if (t == n_tiles - 1) mma_commit(&sm.acc_done);
+          if (t + 1 < n_tiles && !issue_dp(t + 1)) break;
+          if (t + 2 < n_tiles && !issue_s(t + 2, t & 1)) break;
+        }
+      } else {
+        ok = ok && issue_s(0, 0) && issue_dp(0);
+        for (int t = 0; ok && t < n_tiles; ++t) {
+          const int s1 = t % kStagesB1, s2 = t % kStagesB2;
+          if (!mbar_wait(&sm.p_ready, t & 1, ctx, kWPReady)) break;
+          tc_fence_after();
+          issue_acc(kColAcc1, kColS, smem_u32(sm.b2[s2]), t == 0);  // dV += P * dO_t
+          mma_commit(&sm.b2_empty[s2]);
+          if (t + 1 < n_tiles && !issue_s(t + 1, 0)) break;
+          KB_TR(1, t, 5);
+          if (!mbar_wait(&sm.ds_ready[t & 1], (t / 2) & 1, ctx, kWDsReady)) break;
+          KB_TR(1, t, 6);
+          tc_fence_after();
+          issue_acc(kColAcc2, kColDP, smem_u32(sm.b1[s1]), t == 0);  // dK += dS * Q_t
+          mma_commit(&sm.b1_empty[s1]);
+          KB_TR(1, t, 7);
+          if (t == n_tiles - 1) mma_commit(&sm.acc_done);
+          if (t + 1 < n_tiles && !issue_dp(t + 1)) break;
         }
       }
     }
   } else {
     // ------------------------------ compute warps + epilogue ------------------------------
     const int row = (warp & 3) * 32 + lane;
-    const int half = warp >> 2;  // which 32 columns of each 64-column tile this warpgroup owns
+    const int half = warp >> 2;  // which 64 columns of each tile this warpgroup owns
     const int xi = x0 + row;
     // live columns of this row form one interval [lo, hi)
     int lo = 0, hi = 0;
@@ -287,58 +383,84 @@ sa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_a1, const __grid_cons
 
     bool ok = true;
     for (int t = 0; t < n_tiles; ++t) {
-      const int s = t % kStages, buf = t & 1;
-      const int y0 = (yr.begin + t) * kBY + half * 32;  // first column this thread handles
-      ok = __all_sync(0xffffffffu, mbar_wait(&sm.z_ready[buf], (t / 2) & 1, ctx, kWZReady));
+      const int y0 = (yr.begin + t) * kBY + half * 64;  // first column this thread handles
+      const int sbuf = kDQ ? (t & 1) : 0;
+      const uint32_t t_s = t_lane + (sbuf ? kColS1 : kColS) + half * 64;
+      const uint32_t t_dp = t_lane + kColDP + half * 64;
+      const float* lse_c = sm.lse_s[t & 1] + half * 64;
+      const float* delta_c = sm.delta_s[t & 1] + half * 64;
+
+      // ---- phase 1: P = 2^(S * scale - lse) for this thread's 64 columns
+      if (threadIdx.x == 0) KB_TR(2, t, 0);
+      ok = __all_sync(0xffffffffu, mbar_wait(&sm.s_ready[sbuf], kDQ ? (t / 2) & 1 : t & 1, ctx, kWSReady));
+      if (ok && !kDQ) ok = __all_sync(0xffffffffu, mbar_wait(&sm.stats_full[t & 1], (t / 2) & 1, ctx, kWStatsFull));
       if (!ok) break;
       tc_fence_after();
-      const bool warp_full = __all_sync(0xffffffffu, lo <= y0 && y0 + 32 <= hi);
-      const uint32_t t_z1 = t_lane + kColZ1 + buf * kBY, t_z2 = t_lane + kColZ2 + buf * kBY;
-      uint32_t z1[32], z2[32];
-      tmem_ld32(t_z1 + half * 32, z1);
-      tmem_ld32(t_z2 + half * 32, z2);
-      float lse_c[32], delta_c[32];
+      if (threadIdx.x == 0) KB_TR(2, t, 1);
+      const bool warp_full = __all_sync(0xffffffffu, lo <= y0 && y0 + 64 <= hi);
+      float p[64];
+      {
+        uint32_t s[64];
+        tmem_ld32(t_s, reinterpret_cast<uint32_t(&)[32]>(s[0]));
+        tmem_ld32(t_s + 32, reinterpret_cast<uint32_t(&)[32]>(s[32]));
+        tmem_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 64; i += 4) {
+          float4 lv = make_float4(lse_r, lse_r, lse_r, lse_r);
+          if (!kDQ) lv = *reinterpret_cast<const float4*>(lse_c + i);
+          p[i + 0] = ex2_approx(fmaf(__uint_as_float(s[i + 0]), scale, -lv.x));
+          p[i + 1] = ex2_approx(fmaf(__uint_as_float(s[i + 1]), scale, -lv.y));
+          p[i + 2] = ex2_approx(fmaf(__uint_as_float(s[i + 2]), scale, -lv.z));
+          p[i + 3] = ex2_approx(fmaf(__uint_as_float(s[i + 3]), scale, -lv.w));
+        }
+        if (!warp_full) {
+#pragma unroll
+          for (int i = 0; i < 64; ++i) p[i] = (y0 + i >= lo && y0 + i < hi) ? p[i] : 0.f;
+        }
+      }
       if (!kDQ) {
+        // P over the S columns this thread has just consumed, then hand it to the MMA warp
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const float4 lv = *reinterpret_cast<const float4*>(&sm.lse_s[s][half * 32 + 4 * i]);
-          const float4 dv = *reinterpret_cast<const float4*>(&sm.delta_s[s][half * 32 + 4 * i]);
-          lse_c[4 * i] = lv.x, lse_c[4 * i + 1] = lv.y, lse_c[4 * i + 2] = lv.z, lse_c[4 * i + 3] = lv.w;
-          delta_c[4 * i] = dv.x, delta_c[4 * i + 1] = dv.y, delta_c[4 * i + 2] = dv.z, delta_c[4 * i + 3] = dv.w;
+        for (int cc = 0; cc < 2; ++cc) {
+          uint32_t pk[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) pk[i] = pack16x2<BF16>(p[cc * 32 + 2 * i], p[cc * 32 + 2 * i + 1]);
+          tmem_st16(t_s + cc * 16, pk);
+        }
+        tmem_wait_st();
+        tc_fence_before();
+        mbar_arrive(&sm.p_ready);
+      }
+
+      // ---- phase 2: dS = P * (dP - delta)
+      if (threadIdx.x == 0) KB_TR(2, t, 2);
+      ok = __all_sync(0xffffffffu, mbar_wait(&sm.dp_ready, t & 1, ctx, kWDpReady));
+      if (!ok) break;
+      if (threadIdx.x == 0) KB_TR(2, t, 3);
+      tc_fence_after();
+      {
+        uint32_t dp[64];
+        tmem_ld32(t_dp, reinterpret_cast<uint32_t(&)[32]>(dp[0]));
+        tmem_ld32(t_dp + 32, reinterpret_cast<uint32_t(&)[32]>(dp[32]));
+        tmem_wait_ld();
+#pragma unroll
+        for (int cc = 0; cc < 2; ++cc) {
+          uint32_t pk[16];
+#pragma unroll
+          for (int i = 0; i < 16; i += 2) {
+            float4 dv = make_float4(delta_r, delta_r, delta_r, delta_r);
+            if (!kDQ) dv = *reinterpret_cast<const float4*>(delta_c + cc * 32 + 2 * i);
+            const int e = cc * 32 + 2 * i;
+            pk[i] = pack16x2<BF16>(p[e] * (__uint_as_float(dp[e]) - dv.x), p[e + 1] * (__uint_as_float(dp[e + 1]) - dv.y));
+            pk[i + 1] = pack16x2<BF16>(p[e + 2] * (__uint_as_float(dp[e + 2]) - dv.z), p[e + 3] * (__uint_as_float(dp[e + 3]) - dv.w));
+          }
+          tmem_st16(t_dp + cc * 16, pk);
         }
       }
-      tmem_wait_ld();
-      uint32_t pk_p[16], pk_ds[16];
-      if (warp_full) {
-#pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          const float p0 = ex2_approx(fmaf(__uint_as_float(z1[i]), scale, -(kDQ ? lse_r : lse_c[i])));
-          const float p1 = ex2_approx(fmaf(__uint_as_float(z1[i + 1]), scale, -(kDQ ? lse_r : lse_c[i + 1])));
-          const float d0 = p0 * (__uint_as_float(z2[i]) - (kDQ ? delta_r : delta_c[i]));
-          const float d1 = p1 * (__uint_as_float(z2[i + 1]) - (kDQ ? delta_r : delta_c[i + 1]));
-          if (!kDQ) pk_p[i / 2] = pack16x2<BF16>(p0, p1);
-          pk_ds[i / 2] = pack16x2<BF16>(d0, d1);
-        }
-      } else {
-#pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float p0 = ex2_approx(fmaf(__uint_as_float(z1[i]), scale, -(kDQ ? lse_r : lse_c[i])));
-          float p1 = ex2_approx(fmaf(__uint_as_float(z1[i + 1]), scale, -(kDQ ? lse_r : lse_c[i + 1])));
-          p0 = (y0 + i >= lo && y0 + i < hi) ? p0 : 0.f;
-          p1 = (y0 + i + 1 >= lo && y0 + i + 1 < hi) ? p1 : 0.f;
-          const float d0 = p0 * (__uint_as_float(z2[i]) - (kDQ ? delta_r : delta_c[i]));
-          const float d1 = p1 * (__uint_as_float(z2[i + 1]) - (kDQ ? delta_r : delta_c[i + 1]));
-          if (!kDQ) pk_p[i / 2] = pack16x2<BF16>(p0, p1);
-          pk_ds[i / 2] = pack16x2<BF16>(d0, d1);
-        }
-      }
-      // each warpgroup overlays its 16-bit values on the fp32 columns it has just consumed itself
-      // (columns [32 g, 32 g + 16) of the buffer), so the two warpgroups never touch each other's data
-      if (!kDQ) tmem_st16(t_z1 + half * 32, pk_p);
-      tmem_st16(t_z2 + half * 32, pk_ds);
       tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(&sm.p_ready[buf]);
+      mbar_arrive(&sm.ds_ready[t & 1]);
+      if (threadIdx.x == 0) KB_TR(2, t, 4);
     }
 
     if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&sm.acc_done, 0, ctx, kWAccDone));
@@ -391,9 +513,9 @@ int launch_pass(const kb_sa_bwd_params& p, int32_t c, int32_t back, cudaStream_t
   if (!make_tile_map_4d(&tm_a1, a1, p.B, p.H, p.T, D, kBX) || !make_tile_map_4d(&tm_a2, a2, p.B, p.H, p.T, D, kBX) ||
       !make_tile_map_4d(&tm_b1, b1, p.B, p.H, p.T, D, kBY) || !make_tile_map_4d(&tm_b2, b2, p.B, p.H, p.T, D, kBY))
     return KB_ERR_UNSUPPORTED;
-  constexpr bool kWaitZFree = false;
-  auto kern = sa_bwd_sm100_kernel<D, BF16, kDQ, kWaitZFree>;
-  constexpr size_t smem = sizeof(BwdSmem<D>) + 1024;
+  auto kern = sa_bwd_sm100_kernel<D, BF16, kDQ>;
+  constexpr size_t smem = sizeof(BwdSmem<D>);
+  static_assert(sizeof(BwdSmem<D>) <= 232448, "backward shared memory exceeds the 227 KB a CTA may have");
   KB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   BwdArgs a;
   a.o = static_cast<const uint16_t*>(p.o.data);
@@ -437,6 +559,14 @@ int launch_both(const kb_sa_bwd_params& p, int32_t c, int32_t back, cudaStream_t
 }
 
 }  // namespace
+
+#ifdef KB_TRACE
+}  // namespace kb
+extern "C" __attribute__((visibility("default"))) int kb_debug_trace(long long* out) {
+  return (int)cudaMemcpyFromSymbol(out, kb::g_trace, sizeof(kb::g_trace));
+}
+namespace kb {
+#endif
 
 int sa_bwd_sm100(const kb_sa_bwd_params& p, int32_t c, int32_t back, cudaStream_t s) {
   for (void* out : {p.dq, p.dk, p.dv})
