@@ -117,6 +117,23 @@ typedef struct kb_sa_bwd_params {
 KB_API int kb_sa_bwd(const kb_sa_bwd_params* p, void* stream);
 
 /*
+ * Streaming attention backward without caller-provided scratch.  No counterpart in the
+ * reference (its Python op body allocates `delta` itself, kernel.py:1380); it exists for hosts
+ * that cannot allocate device memory around the call: a runtime plugin whose execute hook only
+ * gets input and output bindings, a process that gave all device memory to its own arena, a
+ * latency-bound loop that cannot pay for cudaMalloc's device synchronisation.
+ * Same parameter block as kb_sa_bwd; `delta_ws` is ignored.  The B*H*T floats of delta live in
+ * a fixed array inside the library (KB_NOALLOC_MAX_ROWS floats = 8 MiB per GPU, held until the
+ * process exits); larger problems return KB_ERR_TOO_LARGE and launch nothing.  The first call
+ * on a device resolves the array's address: make it during set-up, before any stream capture
+ * on that device.  All calls on a device share the array (it need not be cleared: each call
+ * overwrites what it reads), so calls that overlap on one GPU race and must be serialised.
+ * Calls no cudaMalloc / cudaFree or allocating library routine.
+ */
+#define KB_NOALLOC_MAX_ROWS (1 << 21)
+KB_API int kb_sa_bwd_noalloc(const kb_sa_bwd_params* p, void* stream);
+
+/*
  * Dense (non-causal) self-attention forward with key padding by `lens`.
  * Replaces the Triton launch in the op body of `alexdremov_flash_attention::forward`
  * (src/self_attention/kernel.py:362-414, kernel `_self_attn_fwd`, lines 125-302).
