@@ -93,18 +93,19 @@ struct alignas(1024) BwdSmem {
   alignas(16) float lse_s[2][kBY];
   alignas(16) float delta_s[2][kBY];
   uint64_t x_full, b1_full[kStagesB1], b1_empty[kStagesB1], b2_full[kStagesB2], b2_empty[kStagesB2];
-  uint64_t s_ready[2], dp_ready, p_ready, ds_ready[2], stats_full[2], acc_done;
+  uint64_t s_ready[2], dp_ready, p_ready, ds_ready[2], stats_full[2], acc_done, staged;
   uint32_t tmem_base;
   int abort_flag;
 };
 
-enum WaitSite { kWX = 21, kWB1Empty, kWB2Empty, kWStats, kWStatsFull, kWB1Full, kWB2Full, kWSReady, kWDpReady, kWPReady, kWDsReady, kWAccDone };
+enum WaitSite { kWX = 21, kWB1Empty, kWB2Empty, kWStats, kWStatsFull, kWB1Full, kWB2Full, kWSReady, kWDpReady, kWPReady, kWDsReady, kWAccDone, kWStaged };
 constexpr int kErrSmemAlign = 41;
 
 template <int D, bool BF16, bool kDQ>
 __global__ void __launch_bounds__(kThreads, 1)
 sa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_a1, const __grid_constant__ CUtensorMap tm_a2,
                     const __grid_constant__ CUtensorMap tm_b1, const __grid_constant__ CUtensorMap tm_b2,
+                    const __grid_constant__ CUtensorMap tm_out1, const __grid_constant__ CUtensorMap tm_out2,
                     const BwdArgs a) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   BwdSmem<D>& sm = *reinterpret_cast<BwdSmem<D>*>(smem_raw);
@@ -168,6 +169,7 @@ sa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_a1, const __grid_cons
     mbar_init(&sm.dp_ready, 1);
     mbar_init(&sm.p_ready, kComputeThreads);
     mbar_init(&sm.acc_done, 1);
+    mbar_init(&sm.staged, kComputeThreads);
     sm.abort_flag = 0;
     fence_mbar_init();
   }
@@ -465,31 +467,47 @@ sa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_a1, const __grid_cons
 
     if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&sm.acc_done, 0, ctx, kWAccDone));
     if (ok) {
+      // Every MMA and every TMA load of this CTA is complete: the B1 ring is free and becomes the
+      // staging area of the outputs (b1[0]: accumulator 1, b1[1]: accumulator 2), in the same
+      // 64-column swizzled panels TMA expects, so that the rows leave as bulk tensor stores
+      // instead of 16-byte stores scattered over 128 rows.
       tc_fence_after();
 #pragma unroll
       for (int which = 0; which < (kDQ ? 1 : 2); ++which) {
         const uint32_t col0 = which == 0 ? kColAcc1 : kColAcc2;
         // dQ and dK carry the softmax scale; dV does not
         const float mul = (kDQ || which == 1) ? a.sm_scale : 1.f;
-        uint16_t* out = which == 0 ? out1 : out2;
+        uint8_t* stage = sm.b1[which];
 #pragma unroll
         for (int cc = 0; cc < D / 64; ++cc) {
-          const int c32 = half * (D / 64) + cc;  // this warpgroup's share of the D columns
+          const int c32 = half * (D / 64) + cc;  // this warpgroup's share of the D columns, 32 at a time
           uint32_t r[32];
           tmem_ld32(t_lane + col0 + c32 * 32, r);
           tmem_wait_ld();
-          if (xi < T) {
-            uint4* dst = reinterpret_cast<uint4*>(out + (int64_t)xi * D + c32 * 32);
+          uint8_t* prow = stage + (c32 / 2) * kPanelBytes + row * 128;
 #pragma unroll
-            for (int g = 0; g < 4; ++g) {
-              uint4 w;
-              w.x = pack16x2<BF16>(__uint_as_float(r[8 * g + 0]) * mul, __uint_as_float(r[8 * g + 1]) * mul);
-              w.y = pack16x2<BF16>(__uint_as_float(r[8 * g + 2]) * mul, __uint_as_float(r[8 * g + 3]) * mul);
-              w.z = pack16x2<BF16>(__uint_as_float(r[8 * g + 4]) * mul, __uint_as_float(r[8 * g + 5]) * mul);
-              w.w = pack16x2<BF16>(__uint_as_float(r[8 * g + 6]) * mul, __uint_as_float(r[8 * g + 7]) * mul);
-              dst[g] = w;
-            }
+          for (int g = 0; g < 4; ++g) {
+            uint4 w;
+            w.x = pack16x2<BF16>(__uint_as_float(r[8 * g + 0]) * mul, __uint_as_float(r[8 * g + 1]) * mul);
+            w.y = pack16x2<BF16>(__uint_as_float(r[8 * g + 2]) * mul, __uint_as_float(r[8 * g + 3]) * mul);
+            w.z = pack16x2<BF16>(__uint_as_float(r[8 * g + 4]) * mul, __uint_as_float(r[8 * g + 5]) * mul);
+            w.w = pack16x2<BF16>(__uint_as_float(r[8 * g + 6]) * mul, __uint_as_float(r[8 * g + 7]) * mul);
+            const int chunk = (c32 & 1) * 4 + g;  // 16-byte chunk within the 128-byte panel row
+            *reinterpret_cast<uint4*>(prow + ((chunk ^ (row & 7)) << 4)) = w;
           }
+        }
+      }
+      fence_proxy_async();
+      mbar_arrive(&sm.staged);
+      if (threadIdx.x == 0) {
+        if (mbar_wait(&sm.staged, 0, ctx, kWStaged)) {
+#pragma unroll
+          for (int which = 0; which < (kDQ ? 1 : 2); ++which)
+#pragma unroll
+            for (int p = 0; p < kPanels; ++p)
+              tma_store_4d(which == 0 ? &tm_out1 : &tm_out2, sm.b1[which] + p * kPanelBytes, p * 64, x0, h, b);
+          tma_store_commit();
+          tma_store_wait_all();
         }
       }
     }
@@ -512,6 +530,10 @@ int launch_pass(const kb_sa_bwd_params& p, int32_t c, int32_t back, cudaStream_t
   const kb_tensor4& b2 = kDQ ? p.v : p.d_o;
   if (!make_tile_map_4d(&tm_a1, a1, p.B, p.H, p.T, D, kBX) || !make_tile_map_4d(&tm_a2, a2, p.B, p.H, p.T, D, kBX) ||
       !make_tile_map_4d(&tm_b1, b1, p.B, p.H, p.T, D, kBY) || !make_tile_map_4d(&tm_b2, b2, p.B, p.H, p.T, D, kBY))
+    return KB_ERR_UNSUPPORTED;
+  CUtensorMap tm_o1, tm_o2;
+  if (!make_tile_map_4d_contiguous(&tm_o1, kDQ ? p.dq : p.dv, p.B, p.H, p.T, D, kBX) ||
+      !make_tile_map_4d_contiguous(&tm_o2, kDQ ? p.dq : p.dk, p.B, p.H, p.T, D, kBX))
     return KB_ERR_UNSUPPORTED;
   auto kern = sa_bwd_sm100_kernel<D, BF16, kDQ>;
   constexpr size_t smem = sizeof(BwdSmem<D>);
@@ -540,7 +562,7 @@ int launch_pass(const kb_sa_bwd_params& p, int32_t c, int32_t back, cudaStream_t
   a.sm_scale = p.sm_scale;
   a.status = p.status;
   dim3 grid(kb_cdiv_i32(p.T, kBX), p.H, p.B);
-  kern<<<grid, kThreads, smem, s>>>(tm_a1, tm_a2, tm_b1, tm_b2, a);
+  kern<<<grid, kThreads, smem, s>>>(tm_a1, tm_a2, tm_b1, tm_b2, tm_o1, tm_o2, a);
   KB_LAUNCH_CHECK(kDQ ? "sa_bwd_sm100_kernel<dq>" : "sa_bwd_sm100_kernel<dkdv>");
   return KB_OK;
 }

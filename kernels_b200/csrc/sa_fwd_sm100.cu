@@ -1,22 +1,35 @@
 // Streaming-attention forward for sm_100a: TMA -> shared memory -> tcgen05.mma -> TMEM.
 //
-// One CTA owns one tile of 128 query rows of one (batch, head) and walks only the live KV
-// tiles (64 keys each) of the streaming schedule (schedule.h).  Six warps, three roles:
-//   warps 0-3  softmax: thread t owns query row t (= TMEM lane t).  Reads a 128 x 64 block of
-//              S from TMEM into registers, keeps the running max / sum, writes P (16-bit) back
-//              over S, rescales O when the max moved by more than 2^8, writes O / LSE at the end;
-//   warp 4     TMA producer (one lane): Q once, then a ring of K/V tiles;
-//   warp 5     MMA issuer (one lane): S = Q K^T (A, B from shared memory), O += P V
+// One CTA owns TWO tiles of 128 query rows (A and B, 256 consecutive rows) of one (batch, head)
+// and walks the live KV tiles (128 keys each) of the streaming schedule (schedule.h); both
+// q tiles use every K/V tile that is brought into shared memory, which halves the L2 traffic
+// per FLOP against one q tile per CTA.  Ten warps, three roles:
+//   warps 0-3 / 4-7  softmax of q tile A / B: thread r owns query row r of its tile (= TMEM lane
+//              r).  Reads a 128 x 128 block of S from TMEM into registers, keeps the running
+//              max / sum, writes P (16-bit) back over S, rescales O when the max moved by more
+//              than 2^8, writes O / LSE at the end;
+//   warp 8     TMA producer (one lane): Q once, then a ring of K tiles and a ring of V tiles;
+//   warp 9     MMA issuer (one lane): S = Q K^T (A, B from shared memory), O += P V
 //              (A = P from TMEM, B = V from shared memory, MN-major); owns the TMEM allocation.
-// S is double buffered in TMEM and the MMA warp issues S(t+1) before P(t) V(t), so the tensor
-// pipe works on one KV tile while the softmax warps are busy with the other.
-// TMEM columns: [0,64) and [64,128) the two S buffers (fp32; P overlays the first 32 columns of
-// each); [128,128+D) O (fp32).  256 columns and ~100 KB of shared memory per CTA keep two CTAs
-// resident per SM.
+// MMA issue order per KV tile t:  PV_A(t-1)  S_A(t)  PV_B(t-1)  S_B(t).  While the softmax warps
+// of one q tile work on their S block the tensor pipe runs the other q tile's MMAs.  MMAs
+// execute in issue order, so S_A(t) may overwrite the P_A(t-1) that PV_A(t-1) reads without a
+// wait, and when S_A(t) is complete so is PV_A(t-1): the softmax warps may rescale O freely.
+// TMEM columns: S_A at 0, S_B at 128 (fp32; P overlays the first 64 columns of each),
+// O_A at 256, O_B at 384.  One CTA per SM.
+//
+// The kernel is persistent: the grid is one CTA per SM and every CTA walks the work items
+// (batch, head, 256-row q block) item = blockIdx.x, blockIdx.x + gridDim.x, ...  Barriers and
+// TMEM are set up once; the producer runs ahead into the next item (its Q is loaded as soon as
+// the last S of the current item has been issued) and the softmax warps write the current
+// item's O while the MMAs of the next one already run, so the pipeline is not drained and
+// refilled per item.  Consecutive items are consecutive q blocks of one (batch, head): the CTAs
+// that run at the same time read neighbouring K/V rows, which keeps them in L2.
 //
 // Masking uses the fact that the live keys of a query row form one interval
 // [max(0, i/c - back) * c, min((i/c + 1) * c, len)), which is the element form of the mask
-// (i < len, j < len, 0 <= i/c - j/c <= back).
+// (i < len, j < len, 0 <= i/c - j/c <= back).  KV tiles that are live for only one of the two
+// q tiles are skipped for the other.
 //
 // Reference semantics: src/streaming_attention/kernel.py:205-430 (online softmax in base 2,
 // P cast to the input type before P V, LSE = m + log2(l)).
@@ -31,43 +44,49 @@ namespace {
 
 using namespace sm100;
 
-constexpr int kBM = 128, kBN = 64;
-constexpr int kStages = 2;
-constexpr int kThreads = 192;
-constexpr uint32_t kTmemCols = 256;
-constexpr uint32_t kColS = 0, kColO = 128;
-constexpr float kRescaleThreshold = 8.f;  // log2 units
+constexpr int kBM = 128;  // rows of one q tile
+constexpr int kQTiles = 2;
+constexpr int kBN = 128;
+constexpr int kStagesK = 3, kStagesV = 2;
+constexpr int kThreads = (kQTiles * 4 + 2) * 32;
+constexpr int kProducerWarp = kQTiles * 4, kMmaWarp = kQTiles * 4 + 1;
+constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kColS = 0, kColO = 256;  // + 128 * q tile
+constexpr float kRescaleThreshold = 8.f;    // log2 units
 
 struct FwdArgs {
   void* o;
   float* lse;
   const int32_t* lens;
   int64_t lens_stride;
-  int32_t H, T, c, back;
+  int32_t B, H, T, c, back;
   float scale_log2;
   int32_t* status;
 };
 
 template <int D>
 struct alignas(1024) FwdSmem {
-  uint8_t q[kBM * D * 2];
-  uint8_t k[kStages][kBN * D * 2];
-  uint8_t v[kStages][kBN * D * 2];
-  uint64_t q_full, k_full[kStages], k_empty[kStages], v_full[kStages], v_empty[kStages], s_ready[2], p_ready[2], pv_done, o_done;
+  uint8_t q[kQTiles][kBM * D * 2];
+  uint8_t k[kStagesK][kBN * D * 2];
+  uint8_t v[kStagesV][kBN * D * 2];
+  uint64_t q_full, k_full[kStagesK], k_empty[kStagesK], v_full[kStagesV], v_empty[kStagesV];
+  uint64_t q_empty, s_ready[kQTiles], p_ready[kQTiles], o_done[kQTiles], o_free[kQTiles];
   uint32_t tmem_base;
   int abort_flag;
 };
 
-enum WaitSite { kWaitQ = 1, kWaitKEmpty, kWaitVEmpty, kWaitKFull, kWaitVFull, kWaitSReady, kWaitPReady, kWaitPvDone, kWaitEpilogue };
+enum WaitSite { kWaitQ = 1, kWaitQEmpty, kWaitOFree, kWaitKEmpty, kWaitVEmpty, kWaitKFull, kWaitVFull, kWaitSReady, kWaitPReady, kWaitEpilogue };
+constexpr int kErrSmemAlign = 11;
 
-// One 128 x 64 block of scores for the thread's row: online softmax update, P into TMEM.
+// One 128 x 128 block of scores for the thread's row: online softmax update, P into TMEM.
 // kMasked = false is the fast path for blocks in which every element of the warp's rows is live.
+// Returns the factor the O accumulator must be multiplied with (1 unless `need_rescale`).
 template <bool BF16, bool kMasked>
-__device__ __forceinline__ void softmax_block(uint32_t t_s, float scale, int k0, int lo, int hi, float& m_used, float& l,
-                                              bool& need_rescale, float& alpha) {
+__device__ __forceinline__ float softmax_block(uint32_t t_s, float scale, int k0, int lo, int hi, float& m_used, float& l,
+                                               bool& need_rescale) {
   uint32_t s[kBN];
-  tmem_ld32(t_s, reinterpret_cast<uint32_t(&)[32]>(s[0]));
-  tmem_ld32(t_s + 32, reinterpret_cast<uint32_t(&)[32]>(s[32]));
+#pragma unroll
+  for (int cc = 0; cc < kBN / 32; ++cc) tmem_ld32(t_s + cc * 32, reinterpret_cast<uint32_t(&)[32]>(s[cc * 32]));
   tmem_wait_ld();
   if (kMasked) {
 #pragma unroll
@@ -85,7 +104,7 @@ __device__ __forceinline__ void softmax_block(uint32_t t_s, float scale, int k0,
   const float m_new = fmaxf(m_used, fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * scale);
   // lazy rescale: keep the old reference maximum unless the new one is > 2^8 larger
   need_rescale = m_new > m_used + kRescaleThreshold;
-  alpha = 1.f;
+  float alpha = 1.f;
   if (need_rescale) {
     alpha = ex2_approx(m_used - m_new);
     m_used = m_new;
@@ -107,206 +126,285 @@ __device__ __forceinline__ void softmax_block(uint32_t t_s, float scale, int k0,
     tmem_st16(t_s + cc * 16, pk);
   }
   l += (sum[0] + sum[1]) + (sum[2] + sum[3]);
+  return alpha;
 }
 
 template <int D, bool BF16>
-__global__ void __launch_bounds__(kThreads, 2)
+__global__ void __launch_bounds__(kThreads, 1)
 sa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                     const __grid_constant__ CUtensorMap tm_v, const FwdArgs a) {
-  extern __shared__ uint8_t smem_raw[];
-  FwdSmem<D>& sm = *reinterpret_cast<FwdSmem<D>*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  FwdSmem<D>& sm = *reinterpret_cast<FwdSmem<D>*>(smem_raw);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int b = blockIdx.z, h = blockIdx.y, q0 = blockIdx.x * kBM;
   const int T = a.T;
-  const int len = a.lens ? kb_clamp_len(a.lens[(int64_t)b * a.lens_stride], T) : T;
-  const int64_t bh = (int64_t)b * a.H + h;
-  uint16_t* o_slice = static_cast<uint16_t*>(a.o) + bh * T * D;
-  float* lse_slice = a.lse ? a.lse + bh * T : nullptr;
+  const int n_qblocks = kb_cdiv_i32(T, kBM * kQTiles);
+  const int n_items = a.B * a.H * n_qblocks;
 
-  const KbTileRange kr = kb_fwd_kv_range(q0, kBM, kBN, len, a.c, a.back);
-  if (kr.begin >= kr.end) {
-    // the whole q tile lies in the padding: its rows are zeros
-    if (threadIdx.x < kBM && q0 + (int)threadIdx.x < T) {
-      uint4* row = reinterpret_cast<uint4*>(o_slice + (int64_t)(q0 + threadIdx.x) * D);
-#pragma unroll
-      for (int i = 0; i < D * 2 / 16; ++i) row[i] = make_uint4(0, 0, 0, 0);
-      if (lse_slice) lse_slice[q0 + threadIdx.x] = 0.f;
+  if (smem_u32(smem_raw) & 1023u) {
+    // swizzled operand tiles need a 1024-byte aligned base: report instead of computing garbage
+    if (threadIdx.x == 0 && a.status) {
+      atomicExch(a.status, KB_ERR_DEVICE_TIMEOUT);
+      atomicExch(a.status + 1, kErrSmemAlign);
     }
     return;
   }
-  const int n_tiles = kr.end - kr.begin;
+
+  // One work item: a 256-row q block of one (batch, head) with the live KV tiles of its two
+  // q tiles and of the block (their union: both ranges are contiguous, B's starts and ends no
+  // earlier than A's, and they touch or overlap).  Every role decodes items the same way.
+  struct Item {
+    int b, h, q0, len;
+    KbTileRange kr[kQTiles];
+    bool act[kQTiles];
+    int u_begin, u_end;
+  };
+  auto decode = [&](int item) {
+    Item it;
+    const int qb = item % n_qblocks, bh = item / n_qblocks;
+    it.b = bh / a.H;
+    it.h = bh - it.b * a.H;
+    it.q0 = qb * (kBM * kQTiles);
+    it.len = a.lens ? kb_clamp_len(a.lens[(int64_t)it.b * a.lens_stride], T) : T;
+#pragma unroll
+    for (int x = 0; x < kQTiles; ++x) {
+      it.kr[x] = kb_fwd_kv_range(it.q0 + x * kBM, kBM, kBN, it.len, a.c, a.back);
+      it.act[x] = it.kr[x].begin < it.kr[x].end;
+    }
+    it.u_begin = it.act[0] ? it.kr[0].begin : it.kr[1].begin;
+    it.u_end = it.act[1] ? it.kr[1].end : it.kr[0].end;
+    return it;
+  };
 
   if (threadIdx.x == 0) {
     mbar_init(&sm.q_full, 1);
-    for (int s = 0; s < kStages; ++s) {
+    mbar_init(&sm.q_empty, 1);
+    for (int s = 0; s < kStagesK; ++s) {
       mbar_init(&sm.k_full[s], 1);
       mbar_init(&sm.k_empty[s], 1);
+    }
+    for (int s = 0; s < kStagesV; ++s) {
       mbar_init(&sm.v_full[s], 1);
       mbar_init(&sm.v_empty[s], 1);
     }
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(&sm.s_ready[i], 1);
-      mbar_init(&sm.p_ready[i], kBM);
+    for (int x = 0; x < kQTiles; ++x) {
+      mbar_init(&sm.s_ready[x], 1);
+      mbar_init(&sm.p_ready[x], kBM);
+      mbar_init(&sm.o_done[x], 1);
+      mbar_init(&sm.o_free[x], kBM);
     }
-    mbar_init(&sm.pv_done, 1);
-    mbar_init(&sm.o_done, 1);
     sm.abort_flag = 0;
     fence_mbar_init();
   }
-  if (warp == 5) tmem_alloc(&sm.tmem_base, kTmemCols);
+  if (warp == kMmaWarp) tmem_alloc(&sm.tmem_base, kTmemCols);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = sm.tmem_base;
   const WaitCtx ctx{&sm.abort_flag, a.status};
-  constexpr uint32_t kQPanelBytes = kBM * 128, kKvPanelBytes = kBN * 128, kKvBytes = kBN * D * 2;
+  constexpr uint32_t kPanelBytes = 128 * 128;  // 128 rows x 128 bytes
+  constexpr uint32_t kTileBytes = 128 * D * 2;
   constexpr int kPanels = D / 64;
 
-  if (warp == 4) {
+  // Barrier phases are counted over the whole life of the CTA: kc / vc = K / V tiles so far,
+  // na = items with at least one live q tile so far, per q tile: tiles and items so far.
+  if (warp == kProducerWarp) {
     // ------------------------------ TMA producer ------------------------------
     if (lane == 0) {
       prefetch_tensormap(&tm_q);
       prefetch_tensormap(&tm_k);
       prefetch_tensormap(&tm_v);
-      mbar_expect_tx(&sm.q_full, kBM * D * 2);
+      int kc = 0, vc = 0, na = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; ok && item < n_items; item += gridDim.x) {
+        const Item it = decode(item);
+        if (!it.act[0] && !it.act[1]) continue;
+        // the Q buffers are free once every S of the previous item has been issued and has run
+        if (na > 0 && !mbar_wait(&sm.q_empty, (na - 1) & 1, ctx, kWaitQEmpty)) break;
+        mbar_expect_tx(&sm.q_full, (it.act[0] ? kTileBytes : 0) + (it.act[1] ? kTileBytes : 0));
 #pragma unroll
-      for (int p = 0; p < kPanels; ++p) tma_load_4d(sm.q + p * kQPanelBytes, &tm_q, &sm.q_full, p * 64, q0, h, b);
-      for (int t = 0; t < n_tiles; ++t) {
-        const int s = t % kStages;
-        const int k0 = (kr.begin + t) * kBN;
-        // K is free again as soon as S(t - kStages) is done, V only after P V: separate rings
-        if (t >= kStages && !mbar_wait(&sm.k_empty[s], ((t / kStages) - 1) & 1, ctx, kWaitKEmpty)) break;
-        mbar_expect_tx(&sm.k_full[s], kKvBytes);
+        for (int x = 0; x < kQTiles; ++x) {
+          if (!it.act[x]) continue;
 #pragma unroll
-        for (int p = 0; p < kPanels; ++p) tma_load_4d(sm.k[s] + p * kKvPanelBytes, &tm_k, &sm.k_full[s], p * 64, k0, h, b);
-        if (t >= kStages && !mbar_wait(&sm.v_empty[s], ((t / kStages) - 1) & 1, ctx, kWaitVEmpty)) break;
-        mbar_expect_tx(&sm.v_full[s], kKvBytes);
+          for (int p = 0; p < kPanels; ++p)
+            tma_load_4d(sm.q[x] + p * kPanelBytes, &tm_q, &sm.q_full, p * 64, it.q0 + x * kBM, it.h, it.b);
+        }
+        for (int t = it.u_begin; t < it.u_end; ++t, ++kc, ++vc) {
+          const int sk = kc % kStagesK, sv = vc % kStagesV;
+          const int k0 = t * kBN;
+          if (kc >= kStagesK && !mbar_wait(&sm.k_empty[sk], ((kc / kStagesK) - 1) & 1, ctx, kWaitKEmpty)) { ok = false; break; }
+          mbar_expect_tx(&sm.k_full[sk], kTileBytes);
 #pragma unroll
-        for (int p = 0; p < kPanels; ++p) tma_load_4d(sm.v[s] + p * kKvPanelBytes, &tm_v, &sm.v_full[s], p * 64, k0, h, b);
+          for (int p = 0; p < kPanels; ++p) tma_load_4d(sm.k[sk] + p * kPanelBytes, &tm_k, &sm.k_full[sk], p * 64, k0, it.h, it.b);
+          if (vc >= kStagesV && !mbar_wait(&sm.v_empty[sv], ((vc / kStagesV) - 1) & 1, ctx, kWaitVEmpty)) { ok = false; break; }
+          mbar_expect_tx(&sm.v_full[sv], kTileBytes);
+#pragma unroll
+          for (int p = 0; p < kPanels; ++p) tma_load_4d(sm.v[sv] + p * kPanelBytes, &tm_v, &sm.v_full[sv], p * 64, k0, it.h, it.b);
+        }
+        ++na;
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == kMmaWarp) {
     // ------------------------------ MMA issuer ------------------------------
     if (lane == 0) {
       constexpr uint32_t idesc_qk = make_idesc(BF16, kBM, kBN, false, false);
       constexpr uint32_t idesc_pv = make_idesc(BF16, kBM, D, false, true);
-      const uint32_t q_addr = smem_u32(sm.q);
-      bool ok = mbar_wait(&sm.q_full, 0, ctx, kWaitQ);
-      for (int t = 0; ok && t <= n_tiles; ++t) {
-        if (t < n_tiles) {
-          // S(t) = Q K_t^T.  Its TMEM buffer was last read by P(t-2) V(t-2), issued earlier by
-          // this thread: MMAs execute in issue order, so no wait is needed for the reuse.
-          const int s = t % kStages, buf = t & 1;
-          if (!mbar_wait(&sm.k_full[s], (t / kStages) & 1, ctx, kWaitKFull)) break;
-          tc_fence_after();
-          const uint32_t k_addr = smem_u32(sm.k[s]);
+      int kbase = 0, na = 0;            // K (= V) tiles of earlier items, live items so far
+      int tiles_x[kQTiles] = {0, 0};    // S / P blocks of q tile x so far
+      int items_x[kQTiles] = {0, 0};    // items in which q tile x was live so far
+      bool ok = true;
+      for (int item = blockIdx.x; ok && item < n_items; item += gridDim.x) {
+        const Item it = decode(item);
+        if (!it.act[0] && !it.act[1]) continue;
+        if (!mbar_wait(&sm.q_full, na & 1, ctx, kWaitQ)) break;
+        // iteration t issues, per q tile x:  PV_x(t-1) then S_x(t)
+        for (int t = it.u_begin; ok && t <= it.u_end; ++t) {
+          const int i = t - it.u_begin;
 #pragma unroll
-          for (int kk = 0; kk < D / 16; ++kk) {
-            const uint32_t qo = (kk / 4) * kQPanelBytes + (kk % 4) * 32, ko = (kk / 4) * kKvPanelBytes + (kk % 4) * 32;
-            mma_ss(tmem + kColS + buf * kBN, desc_kmajor(q_addr + qo), desc_kmajor(k_addr + ko), idesc_qk, kk > 0);
-          }
-          mma_commit(&sm.k_empty[s]);
-          mma_commit(&sm.s_ready[buf]);
-        }
-        if (t >= 1) {
-          const int u = t - 1, s = u % kStages, buf = u & 1;
-          if (!mbar_wait(&sm.p_ready[buf], (u / 2) & 1, ctx, kWaitPReady)) break;
-          if (!mbar_wait(&sm.v_full[s], (u / kStages) & 1, ctx, kWaitVFull)) break;
-          tc_fence_after();
-          const uint32_t v_addr = smem_u32(sm.v[s]);
+          for (int x = 0; x < kQTiles; ++x) {
+            const bool pv_live = t - 1 >= it.kr[x].begin && t - 1 < it.kr[x].end;
+            const bool s_live = t >= it.kr[x].begin && t < it.kr[x].end;
+            if (pv_live) {
+              const int u = t - 1, vi = kbase + i - 1, sv = vi % kStagesV;
+              const int lx = u - it.kr[x].begin;  // index within this q tile's range
+              const int px = tiles_x[x] - 1;  // P block consumed now = last S block issued for x
+              if (!mbar_wait(&sm.p_ready[x], px & 1, ctx, kWaitPReady)) { ok = false; break; }
+              if (!mbar_wait(&sm.v_full[sv], (vi / kStagesV) & 1, ctx, kWaitVFull)) { ok = false; break; }
+              // the first P V of an item overwrites O: the softmax warps must have read the old one
+              if (lx == 0 && items_x[x] > 0 && !mbar_wait(&sm.o_free[x], (items_x[x] - 1) & 1, ctx, kWaitOFree)) { ok = false; break; }
+              tc_fence_after();
+              const uint32_t v_addr = smem_u32(sm.v[sv]);
 #pragma unroll
-          for (int kk = 0; kk < kBN / 16; ++kk) {
-            mma_ts(tmem + kColO, tmem + kColS + buf * kBN + kk * 8, desc_mnmajor(v_addr + kk * 2048, kKvPanelBytes),
-                   idesc_pv, u > 0 || kk > 0);
+              for (int kk = 0; kk < kBN / 16; ++kk) {
+                mma_ts(tmem + kColO + x * 128, tmem + kColS + x * 128 + kk * 8, desc_mnmajor(v_addr + kk * 2048, kPanelBytes),
+                       idesc_pv, lx > 0 || kk > 0);
+              }
+              // V_u is free once the last q tile that uses it has consumed it
+              const bool last_user = (x == kQTiles - 1) || !(u >= it.kr[1].begin && u < it.kr[1].end);
+              if (last_user) mma_commit(&sm.v_empty[sv]);
+              if (u == it.kr[x].end - 1) mma_commit(&sm.o_done[x]);
+            }
+            if (s_live) {
+              const int ki = kbase + i, sk = ki % kStagesK;
+              if (!mbar_wait(&sm.k_full[sk], (ki / kStagesK) & 1, ctx, kWaitKFull)) { ok = false; break; }
+              tc_fence_after();
+              const uint32_t q_addr = smem_u32(sm.q[x]), k_addr = smem_u32(sm.k[sk]);
+#pragma unroll
+              for (int kk = 0; kk < D / 16; ++kk) {
+                const uint32_t off = (kk / 4) * kPanelBytes + (kk % 4) * 32;
+                mma_ss(tmem + kColS + x * 128, desc_kmajor(q_addr + off), desc_kmajor(k_addr + off), idesc_qk, kk > 0);
+              }
+              const bool last_user = (x == kQTiles - 1) || !(t >= it.kr[1].begin && t < it.kr[1].end);
+              if (last_user) mma_commit(&sm.k_empty[sk]);
+              mma_commit(&sm.s_ready[x]);
+              ++tiles_x[x];
+            }
           }
-          mma_commit(&sm.v_empty[s]);
-          mma_commit(&sm.pv_done);
-          if (u == n_tiles - 1) mma_commit(&sm.o_done);
+          if (t == it.u_end - 1) mma_commit(&sm.q_empty);  // every S of this item has been issued
         }
+        kbase += it.u_end - it.u_begin;
+        ++na;
+#pragma unroll
+        for (int x = 0; x < kQTiles; ++x) items_x[x] += it.act[x] ? 1 : 0;
       }
     }
   } else {
     // ------------------------------ softmax + epilogue ------------------------------
-    const int row = threadIdx.x;
-    const int qi = q0 + row;
-    int lo = 0, hi = 0;
-    if (qi < len) {
-      const int qc = qi / a.c;
-      lo = kb_max_i32(0, qc - a.back) * a.c;
-      const int64_t h64 = (int64_t)(qc + 1) * a.c;
-      hi = h64 < len ? (int)h64 : len;
-    }
-    const uint32_t t_lane = tmem + ((uint32_t)(warp * 32) << 16);
+    const int x = warp >> 2;  // q tile of this warpgroup
+    const int row = (warp & 3) * 32 + lane;
+    const uint32_t t_lane = tmem + ((uint32_t)((warp & 3) * 32) << 16);
+    const uint32_t t_s = t_lane + kColS + x * 128, t_o = t_lane + kColO + x * 128;
     const float scale = a.scale_log2;
-    float m_used = -INFINITY, l = 0.f;
+    int tiles = 0, items = 0;  // S blocks / live items of this q tile so far
     bool ok = true;
+    for (int item = blockIdx.x; ok && item < n_items; item += gridDim.x) {
+      const Item it = decode(item);
+      const int qi = it.q0 + x * kBM + row;
+      const int64_t bh = (int64_t)it.b * a.H + it.h;
+      uint16_t* o_row = static_cast<uint16_t*>(a.o) + (bh * T + qi) * D;
+      float* lse_row = a.lse ? a.lse + bh * T + qi : nullptr;
+      if (!it.act[x]) {
+        // this q tile lies wholly in the padding: its rows are zeros
+        if (qi < T) {
+          uint4* dst = reinterpret_cast<uint4*>(o_row);
+#pragma unroll
+          for (int i = 0; i < D * 2 / 16; ++i) dst[i] = make_uint4(0, 0, 0, 0);
+          if (lse_row) *lse_row = 0.f;
+        }
+        continue;
+      }
+      const int n_tiles = it.kr[x].end - it.kr[x].begin;
+      int lo = 0, hi = 0;
+      if (qi < it.len) {
+        const int qc = qi / a.c;
+        lo = kb_max_i32(0, qc - a.back) * a.c;
+        const int64_t h64 = (int64_t)(qc + 1) * a.c;
+        hi = h64 < it.len ? (int)h64 : it.len;
+      }
+      float m_used = -INFINITY, l = 0.f;
 
-    for (int t = 0; t < n_tiles; ++t) {
-      const int buf = t & 1;
-      const int k0 = (kr.begin + t) * kBN;
-      ok = __all_sync(0xffffffffu, mbar_wait(&sm.s_ready[buf], (t / 2) & 1, ctx, kWaitSReady));
-      if (!ok) break;
-      tc_fence_after();
-      const bool warp_full = __all_sync(0xffffffffu, lo <= k0 && k0 + kBN <= hi);
-      bool need;
-      float alpha;
-      if (warp_full)
-        softmax_block<BF16, false>(t_lane + kColS + buf * kBN, scale, k0, lo, hi, m_used, l, need, alpha);
-      else
-        softmax_block<BF16, true>(t_lane + kColS + buf * kBN, scale, k0, lo, hi, m_used, l, need, alpha);
-      if (t > 0 && __any_sync(0xffffffffu, need)) {
-        // O must not be touched while P(t-1) V(t-1) is still accumulating into it
-        ok = __all_sync(0xffffffffu, mbar_wait(&sm.pv_done, (t - 1) & 1, ctx, kWaitPvDone));
+      for (int lx = 0; lx < n_tiles; ++lx, ++tiles) {
+        const int k0 = (it.kr[x].begin + lx) * kBN;
+        ok = __all_sync(0xffffffffu, mbar_wait(&sm.s_ready[x], tiles & 1, ctx, kWaitSReady));
         if (!ok) break;
         tc_fence_after();
+        const bool warp_full = __all_sync(0xffffffffu, lo <= k0 && k0 + kBN <= hi);
+        bool need;
+        float alpha;
+        if (warp_full)
+          alpha = softmax_block<BF16, false>(t_s, scale, k0, lo, hi, m_used, l, need);
+        else
+          alpha = softmax_block<BF16, true>(t_s, scale, k0, lo, hi, m_used, l, need);
+        if (lx > 0 && __any_sync(0xffffffffu, need)) {
+          // S(lx) is complete, so the P V of the previous tile (issued before it) is too: O is idle
 #pragma unroll
-        for (int cc = 0; cc < D / 32; ++cc) {
-          uint32_t r[32];
-          tmem_ld32(t_lane + kColO + cc * 32, r);
-          tmem_wait_ld();
+          for (int cc = 0; cc < D / 32; ++cc) {
+            uint32_t r[32];
+            tmem_ld32(t_o + cc * 32, r);
+            tmem_wait_ld();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-          tmem_st32(t_lane + kColO + cc * 32, r);
-        }
-      }
-      tmem_wait_st();
-      tc_fence_before();
-      mbar_arrive(&sm.p_ready[buf]);
-    }
-
-    // A parity wait on pv_done could be two phases behind here (only P(n-3) V(n-3) is known to be
-    // complete), which a parity bit cannot tell apart: the last accumulation has its own barrier.
-    if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&sm.o_done, 0, ctx, kWaitEpilogue));
-    if (ok) {
-      tc_fence_after();
-      const bool valid = qi < len;
-      const float inv = valid ? 1.f / l : 0.f;
-#pragma unroll
-      for (int cc = 0; cc < D / 32; ++cc) {
-        uint32_t r[32];
-        tmem_ld32(t_lane + kColO + cc * 32, r);
-        tmem_wait_ld();
-        if (qi < T) {
-          uint4* dst = reinterpret_cast<uint4*>(o_slice + (int64_t)qi * D + cc * 32);
-#pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            uint4 w;
-            w.x = pack16x2<BF16>(__uint_as_float(r[8 * g + 0]) * inv, __uint_as_float(r[8 * g + 1]) * inv);
-            w.y = pack16x2<BF16>(__uint_as_float(r[8 * g + 2]) * inv, __uint_as_float(r[8 * g + 3]) * inv);
-            w.z = pack16x2<BF16>(__uint_as_float(r[8 * g + 4]) * inv, __uint_as_float(r[8 * g + 5]) * inv);
-            w.w = pack16x2<BF16>(__uint_as_float(r[8 * g + 6]) * inv, __uint_as_float(r[8 * g + 7]) * inv);
-            dst[g] = w;
+            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+            tmem_st32(t_o + cc * 32, r);
           }
         }
+        tmem_wait_st();
+        tc_fence_before();
+        mbar_arrive(&sm.p_ready[x]);
       }
-      if (lse_slice && qi < T) lse_slice[qi] = valid ? m_used + log2f(l) : 0.f;
+      if (!ok) break;
+
+      ok = __all_sync(0xffffffffu, mbar_wait(&sm.o_done[x], items & 1, ctx, kWaitEpilogue));
+      if (!ok) break;
+      ++items;
+      tc_fence_after();
+      // pull the whole O row out of TMEM, release the accumulator to the next item, then store
+      uint32_t r[D];
+#pragma unroll
+      for (int cc = 0; cc < D / 32; ++cc) tmem_ld32(t_o + cc * 32, reinterpret_cast<uint32_t(&)[32]>(r[cc * 32]));
+      tmem_wait_ld();
+      tc_fence_before();
+      mbar_arrive(&sm.o_free[x]);
+      const bool valid = qi < it.len;
+      const float inv = valid ? 1.f / l : 0.f;
+      if (qi < T) {
+        uint4* dst = reinterpret_cast<uint4*>(o_row);
+#pragma unroll
+        for (int g = 0; g < D / 8; ++g) {
+          uint4 w;
+          w.x = pack16x2<BF16>(__uint_as_float(r[8 * g + 0]) * inv, __uint_as_float(r[8 * g + 1]) * inv);
+          w.y = pack16x2<BF16>(__uint_as_float(r[8 * g + 2]) * inv, __uint_as_float(r[8 * g + 3]) * inv);
+          w.z = pack16x2<BF16>(__uint_as_float(r[8 * g + 4]) * inv, __uint_as_float(r[8 * g + 5]) * inv);
+          w.w = pack16x2<BF16>(__uint_as_float(r[8 * g + 6]) * inv, __uint_as_float(r[8 * g + 7]) * inv);
+          dst[g] = w;
+        }
+        if (lse_row) *lse_row = valid ? m_used + log2f(l) : 0.f;
+      }
     }
   }
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 5) {
+  if (warp == kMmaWarp) {
     if (sm.abort_flag) __nanosleep(1000000);  // let copies still in flight land before the CTA goes away
     tmem_dealloc(tmem, kTmemCols);
   }
@@ -319,20 +417,27 @@ int launch(const kb_sa_fwd_params& p, int32_t c, int32_t back, cudaStream_t s) {
       !make_tile_map_4d(&tm_v, p.v, p.B, p.H, p.T, D, kBN))
     return KB_ERR_UNSUPPORTED;
   auto kern = sa_fwd_sm100_kernel<D, BF16>;
-  constexpr size_t smem = sizeof(FwdSmem<D>) + 1024;
+  constexpr size_t smem = sizeof(FwdSmem<D>);
+  static_assert(sizeof(FwdSmem<D>) <= 232448, "forward shared memory exceeds the 227 KB a CTA may have");
   KB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   FwdArgs a;
   a.o = p.o;
   a.lse = p.lse;
   a.lens = p.lens;
   a.lens_stride = p.lens_stride;
+  a.B = p.B;
   a.H = p.H;
   a.T = p.T;
   a.c = c;
   a.back = back;
   a.scale_log2 = p.sm_scale * kLog2e;
   a.status = p.status;
-  dim3 grid(kb_cdiv_i32(p.T, kBM), p.H, p.B);
+  const int64_t n_items = (int64_t)p.B * p.H * kb_cdiv_i32(p.T, kBM * kQTiles);
+  if (n_items > (int64_t)1 << 30) return KB_ERR_TOO_LARGE;
+  int dev = 0, n_sm = 0;
+  KB_CUDA_TRY(cudaGetDevice(&dev));
+  KB_CUDA_TRY(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev));
+  const unsigned grid = (unsigned)(n_items < n_sm ? n_items : n_sm);  // persistent: one CTA per SM
   kern<<<grid, kThreads, smem, s>>>(tm_q, tm_k, tm_v, a);
   KB_LAUNCH_CHECK("sa_fwd_sm100_kernel");
   return KB_OK;

@@ -52,4 +52,15 @@ inline bool make_tile_map_4d(CUtensorMap* out, const kb_tensor4& t, int B, int H
   return r == CUDA_SUCCESS;
 }
 
+// Map over a contiguous 16-bit [B, H, T, D] output tensor (same boxes as the inputs).
+inline bool make_tile_map_4d_contiguous(CUtensorMap* out, void* data, int B, int H, int T, int D, int box_rows) {
+  kb_tensor4 t;
+  t.data = data;
+  t.stride[3] = 1;
+  t.stride[2] = D;
+  t.stride[1] = (int64_t)T * D;
+  t.stride[0] = (int64_t)H * T * D;
+  return make_tile_map_4d(out, t, B, H, T, D, box_rows);
+}
+
 }  // namespace kb
