@@ -164,7 +164,7 @@ sa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_a1, const __grid_cons
     for (int i = 0; i < 2; ++i) {
       mbar_init(&sm.s_ready[i], 1);
       mbar_init(&sm.ds_ready[i], kComputeThreads);
-      mbar_init(&sm.stats_full[i], 32);
+      mbar_init(&sm.stats_full[i], kDQ ? kComputeThreads : 32);
     }
     mbar_init(&sm.dp_ready, 1);
     mbar_init(&sm.p_ready, kComputeThreads);
@@ -349,42 +349,62 @@ sa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_a1, const __grid_cons
     const float scale = a.scale_log2;
 
     float lse_r = 0.f, delta_r = 0.f;
+    bool ok = true;
     if (kDQ) {
-      if (xi < len) {
-        const uint4* orow = reinterpret_cast<const uint4*>(a.o + b * a.o_sb + h * a.o_sh + (int64_t)xi * a.o_st);
-        const uint4* grow = reinterpret_cast<const uint4*>(a.d_o + b * a.do_sb + h * a.do_sh + (int64_t)xi * a.do_st);
-        float part[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll 4
-        for (int i = 0; i < D * 2 / 16; ++i) {
-          const uint4 ov = __ldg(orow + i), gv = __ldg(grow + i);
-          const uint32_t ow[4] = {ov.x, ov.y, ov.z, ov.w}, gw[4] = {gv.x, gv.y, gv.z, gv.w};
+      // delta = rowsum(O * dO) for the 128 rows of the tile, read cooperatively: a group of D/8
+      // lanes reads one row as 16-byte chunks (fully coalesced), warp w covers rows 16 w .. 16 w + 15,
+      // and the row sums travel to their owner threads through shared memory.
+      constexpr int kLanesPerRow = D / 8, kRowsPerIter = 32 / kLanesPerRow, kIters = 16 / kRowsPerIter;
+      const int sub = lane / kLanesPerRow, chunk = lane % kLanesPerRow;
+      const uint16_t* o_base = a.o + b * a.o_sb + h * a.o_sh;
+      const uint16_t* g_base = a.d_o + b * a.do_sb + h * a.do_sh;
+      uint4 ov[kIters], gv[kIters];
 #pragma unroll
-          for (int w = 0; w < 4; ++w) {
-            float o0, o1, g0, g1;
-            if (BF16) {
-              o0 = __uint_as_float(ow[w] << 16);
-              o1 = __uint_as_float(ow[w] & 0xffff0000u);
-              g0 = __uint_as_float(gw[w] << 16);
-              g1 = __uint_as_float(gw[w] & 0xffff0000u);
-            } else {
-              const __half2 oh = *reinterpret_cast<const __half2*>(&ow[w]), gh = *reinterpret_cast<const __half2*>(&gw[w]);
-              o0 = __low2float(oh);
-              o1 = __high2float(oh);
-              g0 = __low2float(gh);
-              g1 = __high2float(gh);
-            }
-            part[w] = fmaf(o0, g0, part[w]);
-            part[w] = fmaf(o1, g1, part[w]);
-          }
+      for (int it = 0; it < kIters; ++it) {
+        const int r = x0 + 16 * warp + it * kRowsPerIter + sub;
+        ov[it] = gv[it] = make_uint4(0, 0, 0, 0);
+        if (r < len) {
+          ov[it] = __ldg(reinterpret_cast<const uint4*>(o_base + (int64_t)r * a.o_st) + chunk);
+          gv[it] = __ldg(reinterpret_cast<const uint4*>(g_base + (int64_t)r * a.do_st) + chunk);
         }
-        delta_r = (part[0] + part[1]) + (part[2] + part[3]);
-        lse_r = a.lse[bh * T + xi];
       }
-      if (half == 0 && xi < T) a.delta[bh * T + xi] = delta_r;
+#pragma unroll
+      for (int it = 0; it < kIters; ++it) {
+        const uint32_t ow[4] = {ov[it].x, ov[it].y, ov[it].z, ov[it].w}, gw[4] = {gv[it].x, gv[it].y, gv[it].z, gv[it].w};
+        float part = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+          float o0, o1, g0, g1;
+          if (BF16) {
+            o0 = __uint_as_float(ow[w] << 16);
+            o1 = __uint_as_float(ow[w] & 0xffff0000u);
+            g0 = __uint_as_float(gw[w] << 16);
+            g1 = __uint_as_float(gw[w] & 0xffff0000u);
+          } else {
+            const __half2 oh = *reinterpret_cast<const __half2*>(&ow[w]), gh = *reinterpret_cast<const __half2*>(&gw[w]);
+            o0 = __low2float(oh);
+            o1 = __high2float(oh);
+            g0 = __low2float(gh);
+            g1 = __high2float(gh);
+          }
+          part = fmaf(o0, g0, part);
+          part = fmaf(o1, g1, part);
+        }
+#pragma unroll
+        for (int off = kLanesPerRow / 2; off > 0; off >>= 1) part += __shfl_xor_sync(0xffffffffu, part, off);
+        if (chunk == 0) {
+          const int rr = 16 * warp + it * kRowsPerIter + sub;
+          sm.delta_s[0][rr] = part;
+          if (x0 + rr < T) a.delta[bh * T + x0 + rr] = part;
+        }
+      }
+      mbar_arrive(&sm.stats_full[0]);
+      if (xi < len) lse_r = a.lse[bh * T + xi];
+      ok = __all_sync(0xffffffffu, mbar_wait(&sm.stats_full[0], 0, ctx, kWStatsFull));
+      delta_r = sm.delta_s[0][row];
     }
 
-    bool ok = true;
-    for (int t = 0; t < n_tiles; ++t) {
+    for (int t = 0; ok && t < n_tiles; ++t) {
       const int y0 = (yr.begin + t) * kBY + half * 64;  // first column this thread handles
       const int sbuf = kDQ ? (t & 1) : 0;
       const uint32_t t_s = t_lane + (sbuf ? kColS1 : kColS) + half * 64;
