@@ -56,6 +56,11 @@ WORKLOADS = {
 }
 TORCH_DTYPES = {"bf16": torch.bfloat16, "f16": torch.float16, "f32": torch.float32}
 
+# dram__bytes_read.sum + dram__bytes_write.sum of the dK/dV pass per (batch, head) slice of T=16384, D=128,
+# c=256, back=2, lens=T, from the ncu capture of workload `prof` (32 slices, 782 MB; traffic is proportional to the
+# number of slices: every slice reads Q, K, V, dO once and writes dK, dV once).
+NCU_DKDV_TRAFFIC_PER_SLICE = {"cfg3": 782e6 / 32, "prof": 782e6 / 32}
+
 
 def _peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
@@ -380,7 +385,10 @@ def run_own(args, w):
             "kernel_tflops": {"fwd": 4.0 * D * pairs_local / k_ms[0] / 1e9, "bwd_dq": 2.0 * D * pairs_local / k_ms[1] / 1e9,
                               "bwd_dkdv": achieved},
             "roofline": {"kernel": "backward dK/dV pass", "bound": "tensor", "achieved": achieved, "peak": peak,
-                         "unit": "TFLOP/s", "frac": achieved / peak, "peak_source": peaks["source"], "traffic": None,
+                         "unit": "TFLOP/s", "frac": achieved / peak, "peak_source": peaks["source"],
+                         "traffic": (NCU_DKDV_TRAFFIC_PER_SLICE[args.workload] * B * len(heads)
+                                     if args.workload in NCU_DKDV_TRAFFIC_PER_SLICE else None),
+                         "algorithmic_flops_per_launch": dkdv_flops,
                          "hbm_min_bytes_fwd_bwd": 12 * rows_local * D * el + 8 * rows_local,
                          "hbm_frac_if_min_traffic": (12 * rows_local * D * el + 8 * rows_local) / (ms_per_step * 1e-3) / 1e9
                          / peaks["hbm_gbs"]},
@@ -398,16 +406,72 @@ def run_own(args, w):
         dist.destroy_process_group()
 
 
+def run_dense(args):
+    """BASELINE.json configs[3]: dense self-attention forward (fp16 B=16 H=16 T=2048 D=64, key padding
+    lens ~ U[1024, 2048]) and row softmax (fp32 [65536, 4096] ~ N(0, 4)), one GPU.  Each iteration is
+    timed with its own event pair; a 512 MB buffer is rewritten between iterations to flush L2."""
+    from kernels_b200 import _lib, synthetic
+    from kernels_b200.self_attention import self_attention
+    from kernels_b200.softmax import softmax
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    peaks = _peaks()
+    flush = torch.empty(512 * 1024 * 1024, dtype=torch.uint8, device=dev)
+
+    def timed(fn, steps, warmup):
+        for _ in range(max(warmup, 3)):
+            fn()
+        ts = []
+        for _ in range(steps):
+            flush.fill_(1)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1))
+        return statistics.median(ts)
+
+    B, H, T, D = 16, 16, 2048, 64
+    g = torch.Generator(device=dev).manual_seed(0)
+    q, k, v = (torch.randn(B, H, T, D, device=dev, generator=g).half() for _ in range(3))
+    lens = synthetic.make_lens(B, 1024, 2048, seed=0).to(dev)
+    launches0 = _lib.launch_count()
+    with ClockSampler(0) as clk:
+        fa_ms = timed(lambda: self_attention(q, k, v, lens), args.steps, args.warmup)
+        x = torch.randn(65536, 4096, device=dev, generator=g) * 2.0
+        sm_ms = timed(lambda: softmax(x), args.steps, args.warmup)
+    fa_flops = 4.0 * D * H * float((lens.double() ** 2).sum())
+    sm_bytes = 2.0 * x.numel() * 4
+    line = {
+        "metric": "dense self-attention fwd useful TFLOP/s; row softmax GB/s", "value": fa_flops / fa_ms / 1e9,
+        "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": fa_ms,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "impl": "kernels_b200",
+        "config": {"workload": "fp16 B=16 H=16 T=2048 D=64 non-causal lens~U[1024,2048]; softmax fp32 [65536,4096]",
+                   "name": "cfg4", "l2": "flushed between iterations (512 MB write)"},
+        "softmax": {"ms": sm_ms, "gbs": sm_bytes / sm_ms / 1e6, "algorithmic_bytes": sm_bytes},
+        "roofline": {"kernel": "softmax_rows_kernel", "bound": "hbm", "achieved": sm_bytes / sm_ms / 1e6,
+                     "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": sm_bytes / sm_ms / 1e6 / peaks["hbm_gbs"],
+                     "peak_source": peaks["source"], "traffic": None},
+        "gpu_launches": _lib.launch_count() - launches0, "clocks": clk.summary(),
+    }
+    print(json.dumps(line))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--workload", default="cfg3", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="cfg3", choices=sorted(WORKLOADS) + ["cfg4"])
     ap.add_argument("--impl", default="own", choices=["own", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     args = ap.parse_args()
+    if args.workload == "cfg4":
+        return run_dense(args)
     w = WORKLOADS[args.workload]
     if args.impl == "reference":
         run_reference(args, w)

@@ -154,15 +154,22 @@ int kb_sa_tile_config(int32_t dtype, int32_t D, int32_t context_size, uint32_t f
   int32_t pth = KB_PATH_GENERIC, tq = D <= 128 ? 64 : 32, tk = tq, st = 1;
 #ifdef KB_HAVE_SM100
   if (kb::sm100_shape_ok(dtype, D, flags) && unit_inner_stride) {
-#ifndef KB_HAVE_SM100_BWD
-    if (which == 0)
-#endif
-    {
+    // forward: two 128-row q tiles per CTA share 128-key K/V tiles (K ring 3 deep, V ring 2 deep);
+    // backward passes: 128 stationary rows, 128-row streamed tiles (rings 3 and 2 deep)
+    if (which == 0) {
+      pth = KB_PATH_SM100;
+      tq = 256;
+      tk = 128;
+      st = 3;
+    }
+#ifdef KB_HAVE_SM100_BWD
+    if (which != 0) {
       pth = KB_PATH_SM100;
       tq = 128;
       tk = 128;
-      st = (D == 64) ? 4 : 2;
+      st = 3;
     }
+#endif
   }
 #else
   (void)flags;
