@@ -59,7 +59,7 @@ TORCH_DTYPES = {"bf16": torch.bfloat16, "f16": torch.float16, "f32": torch.float
 # dram__bytes_read.sum + dram__bytes_write.sum of the dK/dV pass per (batch, head) slice of T=16384, D=128,
 # c=256, back=2, lens=T, from the ncu capture of workload `prof` (32 slices, 782 MB; traffic is proportional to the
 # number of slices: every slice reads Q, K, V, dO once and writes dK, dV once).
-NCU_DKDV_TRAFFIC_PER_SLICE = {"cfg3": 782e6 / 32, "prof": 782e6 / 32}
+NCU_TRAFFIC_PER_SLICE = {"bwd_dkdv_pass": {"cfg3": 782e6 / 32, "prof": 782e6 / 32}}
 
 
 def _peaks():
@@ -215,8 +215,10 @@ def run_reference(args, w):
 # ------------------------------------------------------------------------------------------
 # own arm
 # ------------------------------------------------------------------------------------------
-def _bwd_params(lib_mod, q, k, v, o, do, lse, dq, dk, dv, delta, lens, w, flags):
+def _bwd_params(lib_mod, q, k, v, o, do, lse, dq, dk, dv, delta, lens, w, flags, ds_ws=None):
     p = lib_mod.SaBwdParams()
+    if ds_ws is not None:
+        p.ds_ws, p.ds_ws_bytes = ds_ws.data_ptr(), ds_ws.numel()
     p.q, p.k, p.v, p.o, p.d_o = (lib_mod.tensor4(t) for t in (q, k, v, o, do))
     p.lse, p.dq, p.dk, p.dv, p.delta_ws = lse.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), delta.data_ptr()
     p.lens = lens.data_ptr() if lens is not None else None
@@ -276,13 +278,24 @@ def run_own(args, w):
     fp.dtype = _lib.dtype_code(dtype)
     fp.context_size, fp.back_contexts, fp.sm_scale, fp.flags = w["c"], w["back"], scale, 0
     fp.status = _lib.status_words().data_ptr()
-    bp_dq = _bwd_params(_lib, q, k, v, o, do, lse, dq, dk, dv, delta, lens_d, w, _lib.KB_FLAG_BWD_SKIP_DKDV)
-    bp_dkdv = _bwd_params(_lib, q, k, v, o, do, lse, dq, dk, dv, delta, lens_d, w, _lib.KB_FLAG_BWD_SKIP_DQ)
+    # backward: the single-evaluation kernels (delta, main = dK/dV/dS, dQ from the saved dS tiles), one
+    # C-ABI call per kernel so that each can be timed; --two-pass times the dQ pass + dK/dV pass instead
+    SKIP_DELTA, SKIP_MAIN, SKIP_DQ = _lib.KB_FLAG_BWD_SKIP_DELTA, _lib.KB_FLAG_BWD_SKIP_DKDV, _lib.KB_FLAG_BWD_SKIP_DQ
+    if args.two_pass:
+        kernel_names = ("fwd", "bwd_dq_pass", "bwd_dkdv_pass")
+        bwd_calls = [_bwd_params(_lib, q, k, v, o, do, lse, dq, dk, dv, delta, lens_d, w, f | _lib.KB_FLAG_BWD_TWO_PASS)
+                     for f in (SKIP_MAIN, SKIP_DQ)]
+    else:
+        ws_bytes = int(lib.kb_sa_bwd_workspace_bytes(*q.shape, _lib.dtype_code(dtype), w["c"], w["back"]))
+        ds_ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
+        kernel_names = ("fwd", "bwd_delta", "bwd_main", "bwd_dq")
+        bwd_calls = [_bwd_params(_lib, q, k, v, o, do, lse, dq, dk, dv, delta, lens_d, w, f, ds_ws)
+                     for f in (SKIP_MAIN | SKIP_DQ, SKIP_DELTA | SKIP_DQ, SKIP_DELTA | SKIP_MAIN)]
     stream = torch.cuda.current_stream(dev)
 
     def step(events=None):
         marks = []
-        for fn, prm in ((lib.kb_sa_fwd, fp), (lib.kb_sa_bwd, bp_dq), (lib.kb_sa_bwd, bp_dkdv)):
+        for fn, prm in [(lib.kb_sa_fwd, fp)] + [(lib.kb_sa_bwd, b_) for b_ in bwd_calls]:
             if events is not None:
                 e0 = torch.cuda.Event(enable_timing=True)
                 e0.record(stream)
@@ -324,7 +337,8 @@ def run_own(args, w):
     elapsed_ms = float(t.item())
     ms_per_step = elapsed_ms / args.steps
     value = flops_total / (ms_per_step * 1e-3) / 1e12
-    k_ms = [statistics.mean(m[i][0].elapsed_time(m[i][1]) for m in per_kernel) for i in range(3)]
+    k_ms = {name: statistics.mean(m[i][0].elapsed_time(m[i][1]) for m in per_kernel)
+            for i, name in enumerate(kernel_names)}
 
     # ---- end to end through the public API with host buffers ----
     qd, kd, vd = (torch.empty_like(q).requires_grad_() for _ in range(3))
@@ -364,9 +378,12 @@ def run_own(args, w):
     if rank == 0:
         peaks = _peaks()
         peak = peaks["tflops_sustained"] if ms_per_step * args.steps > 500 else peaks["tflops"]
-        # dominant kernel: the dK/dV pass; its algorithmic work is the 4 matmuls it cannot avoid
+        # dominant kernel: the one that forms dK and dV (and, in the single-evaluation family, saves
+        # dS); its algorithmic work is the 4 matmuls S, dP, dV, dK
+        dom = "bwd_dkdv_pass" if args.two_pass else "bwd_main"
         dkdv_flops = 8.0 * D * pairs_local
-        achieved = dkdv_flops / (k_ms[2] * 1e-3) / 1e12
+        achieved = dkdv_flops / (k_ms[dom] * 1e-3) / 1e12
+        k_flops = {"fwd": 4.0, "bwd_dq_pass": 2.0, "bwd_dkdv_pass": 8.0, "bwd_main": 8.0, "bwd_dq": 2.0}
         el = q.element_size()
         line = {
             "metric": "streaming-attn fwd+bwd useful TFLOP/s", "value": value, "unit": "TFLOP/s",
@@ -381,13 +398,13 @@ def run_own(args, w):
             "frac_of_bf16_peak": {"measured_burst": value / world / peaks["tflops"],
                                   "measured_sustained": value / world / peaks["tflops_sustained"],
                                   "spec_2250": value / world / 2250.0},
-            "kernel_ms": {"fwd": k_ms[0], "bwd_dq": k_ms[1], "bwd_dkdv": k_ms[2]},
-            "kernel_tflops": {"fwd": 4.0 * D * pairs_local / k_ms[0] / 1e9, "bwd_dq": 2.0 * D * pairs_local / k_ms[1] / 1e9,
-                              "bwd_dkdv": achieved},
-            "roofline": {"kernel": "backward dK/dV pass", "bound": "tensor", "achieved": achieved, "peak": peak,
+            "kernel_ms": k_ms,
+            "kernel_tflops": {n_: k_flops[n_] * D * pairs_local / ms_ / 1e9 for n_, ms_ in k_ms.items() if n_ in k_flops},
+            "roofline": {"kernel": "backward dK/dV pass" if args.two_pass else "backward main kernel (dK, dV, dS)",
+                         "bound": "tensor", "achieved": achieved, "peak": peak,
                          "unit": "TFLOP/s", "frac": achieved / peak, "peak_source": peaks["source"],
-                         "traffic": (NCU_DKDV_TRAFFIC_PER_SLICE[args.workload] * B * len(heads)
-                                     if args.workload in NCU_DKDV_TRAFFIC_PER_SLICE else None),
+                         "traffic": (NCU_TRAFFIC_PER_SLICE[dom][args.workload] * B * len(heads)
+                                     if args.workload in NCU_TRAFFIC_PER_SLICE.get(dom, {}) else None),
                          "algorithmic_flops_per_launch": dkdv_flops,
                          "hbm_min_bytes_fwd_bwd": 12 * rows_local * D * el + 8 * rows_local,
                          "hbm_frac_if_min_traffic": (12 * rows_local * D * el + 8 * rows_local) / (ms_per_step * 1e-3) / 1e9
@@ -469,6 +486,8 @@ def main():
     ap.add_argument("--impl", default="own", choices=["own", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
+    ap.add_argument("--two-pass", action="store_true",
+                    help="time the two-pass backward (dQ pass + dK/dV pass) instead of the single-evaluation kernels")
     args = ap.parse_args()
     if args.workload == "cfg4":
         return run_dense(args)

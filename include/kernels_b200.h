@@ -50,10 +50,17 @@ typedef enum kb_dtype { KB_F32 = 0, KB_F16 = 1, KB_BF16 = 2 } kb_dtype;
 #define KB_FLAG_PRESCALE_QK 1u   /* accepted for signature parity; scaling is always done in fp32 */
 #define KB_FLAG_ALLOW_TF32 2u    /* precision="tf32": accepted, fp32 inputs still use IEEE fp32    */
 #define KB_FLAG_FORCE_GENERIC 4u /* skip the tcgen05 path even where it applies (tests)           */
-/* backward only, for per-kernel timing: run one of the two passes.  The dK/dV pass reads the
- * delta a previous dQ pass over the same inputs left in delta_ws. */
+/* backward only, for per-kernel timing: leave out kernels of the backward.  A kernel that runs
+ * reads what an earlier call over the same inputs left in delta_ws / ds_ws.
+ *   two-pass kernels:          SKIP_DQ = no dQ pass (which also forms delta), SKIP_DKDV = no dK/dV pass
+ *   single-evaluation kernels: SKIP_DELTA = no delta kernel, SKIP_DKDV = no main kernel (dK, dV, dS),
+ *                              SKIP_DQ = no dQ kernel */
 #define KB_FLAG_BWD_SKIP_DQ 8u
 #define KB_FLAG_BWD_SKIP_DKDV 16u
+#define KB_FLAG_BWD_SKIP_DELTA 64u
+/* backward only: always take the two-pass kernels (dQ pass + dK/dV pass, no scratch besides delta)
+ * even when ds_ws is given */
+#define KB_FLAG_BWD_TWO_PASS 32u
 
 /* which kernel family an attention call resolves to (see kb_sa_select_path) */
 #define KB_PATH_GENERIC 0 /* CUDA-core path: any dtype, head_dim, stride                 */
@@ -92,8 +99,16 @@ KB_API int kb_sa_fwd(const kb_sa_fwd_params* p, void* stream);
  * Streaming attention backward: dQ, dK, dV from (q, k, v, o, lse, do).
  * Replaces both launches in `attention_backward_adapter`
  * (src/streaming_attention/kernel.py:1363-1442: `_streaming_attn_bwd_precompute`, lines
- * 453-514, and `_streaming_attn_bwd`, lines 530-635).  delta = rowsum(o * do) is computed
- * inside the dQ pass and handed to the dK/dV pass through `delta_ws`.
+ * 453-514, and `_streaming_attn_bwd`, lines 530-635).
+ * Two kernel families serve 16-bit inputs with D in {64, 128}; both are free of atomics and
+ * bitwise repeatable:
+ *   - single evaluation (taken when `ds_ws` is given and KB_FLAG_BWD_TWO_PASS is not set): a small
+ *     kernel forms delta = rowsum(o * do); one persistent kernel walks the transposed schedule
+ *     once, produces dK and dV and leaves every 16-bit dS tile in the scratch `ds_ws`; a second
+ *     persistent kernel turns the saved tiles into dQ.  Five matmuls per tile pair;
+ *   - two passes (`ds_ws` NULL, too small, or KB_FLAG_BWD_TWO_PASS): a dQ pass that also forms delta
+ *     and a dK/dV pass, each recomputing the scores: seven matmuls per tile pair, no scratch but
+ *     delta.
  * Rows t >= len_b of dq, dk, dv are written as 0.
  */
 typedef struct kb_sa_bwd_params {
@@ -112,9 +127,19 @@ typedef struct kb_sa_bwd_params {
   float sm_scale;
   uint32_t flags;
   int32_t* status;
+  void* ds_ws;          /* scratch of kb_sa_bwd_workspace_bytes() bytes, 16-byte aligned, or NULL */
+  uint64_t ds_ws_bytes; /* its size; too small a scratch selects the two-pass kernels          */
 } kb_sa_bwd_params;
 
 KB_API int kb_sa_bwd(const kb_sa_bwd_params* p, void* stream);
+
+/* Host-only: bytes of `ds_ws` the single-evaluation backward needs for this problem: one 32 KB
+ * tile per (key tile, query tile) slot, B * H * ceil(T / 128) * W tiles with W the most query tiles
+ * a 128-row key tile meets under (context_size, back_contexts).  0 when no such kernel covers
+ * (dtype, D).  The amount grows with (back_contexts + 1) * context_size: a caller that finds it too
+ * large passes ds_ws = NULL and gets the two-pass kernels. */
+KB_API uint64_t kb_sa_bwd_workspace_bytes(int32_t B, int32_t H, int32_t T, int32_t D, int32_t dtype,
+                                          int32_t context_size, int32_t back_contexts);
 
 /*
  * Streaming attention backward without caller-provided scratch.  No counterpart in the
@@ -122,7 +147,8 @@ KB_API int kb_sa_bwd(const kb_sa_bwd_params* p, void* stream);
  * that cannot allocate device memory around the call: a runtime plugin whose execute hook only
  * gets input and output bindings, a process that gave all device memory to its own arena, a
  * latency-bound loop that cannot pay for cudaMalloc's device synchronisation.
- * Same parameter block as kb_sa_bwd; `delta_ws` is ignored.  The B*H*T floats of delta live in
+ * Same parameter block as kb_sa_bwd; `delta_ws` and `ds_ws` are ignored (the two-pass kernels
+ * run, which need no other scratch).  The B*H*T floats of delta live in
  * a fixed array inside the library (KB_NOALLOC_MAX_ROWS floats = 8 MiB per GPU, held until the
  * process exits); larger problems return KB_ERR_TOO_LARGE and launch nothing.  The first call
  * on a device resolves the array's address: make it during set-up, before any stream capture

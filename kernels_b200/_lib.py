@@ -17,14 +17,14 @@ LIB_PATH = os.path.join(_PKG_DIR, "lib", "libkernels_b200.so")
 KB_STATUS_WORDS = 4
 KB_F32, KB_F16, KB_BF16 = 0, 1, 2
 KB_FLAG_PRESCALE_QK, KB_FLAG_ALLOW_TF32, KB_FLAG_FORCE_GENERIC = 1, 2, 4
-KB_FLAG_BWD_SKIP_DQ, KB_FLAG_BWD_SKIP_DKDV = 8, 16
+KB_FLAG_BWD_SKIP_DQ, KB_FLAG_BWD_SKIP_DKDV, KB_FLAG_BWD_TWO_PASS, KB_FLAG_BWD_SKIP_DELTA = 8, 16, 32, 64
 KB_PATH_GENERIC, KB_PATH_SM100 = 0, 1
 KB_NOALLOC_MAX_ROWS = 1 << 21
 
 _DTYPES = {torch.float32: KB_F32, torch.float16: KB_F16, torch.bfloat16: KB_BF16}
 
 EXPORTS = (
-    "kb_sa_fwd", "kb_sa_bwd", "kb_sa_bwd_noalloc", "kb_fa_fwd", "kb_softmax_fwd", "kb_sa_plan", "kb_sa_tile_config",
+    "kb_sa_fwd", "kb_sa_bwd", "kb_sa_bwd_workspace_bytes", "kb_sa_bwd_noalloc", "kb_fa_fwd", "kb_softmax_fwd", "kb_sa_plan", "kb_sa_tile_config",
     "kb_launch_count", "kb_strerror", "kb_last_cuda_error", "kb_version",
 )
 
@@ -53,6 +53,7 @@ class SaBwdParams(C.Structure):
         ("B", C.c_int32), ("H", C.c_int32), ("T", C.c_int32), ("D", C.c_int32),
         ("dtype", C.c_int32), ("context_size", C.c_int32), ("back_contexts", C.c_int32),
         ("sm_scale", C.c_float), ("flags", C.c_uint32), ("status", C.c_void_p),
+        ("ds_ws", C.c_void_p), ("ds_ws_bytes", C.c_uint64),
     ]
 
 
@@ -82,6 +83,8 @@ def load() -> C.CDLL:
     lib.kb_sa_bwd.argtypes = [C.POINTER(SaBwdParams), C.c_void_p]
     lib.kb_sa_bwd_noalloc.argtypes = [C.POINTER(SaBwdParams), C.c_void_p]
     lib.kb_sa_bwd_noalloc.restype = C.c_int
+    lib.kb_sa_bwd_workspace_bytes.argtypes = [C.c_int32] * 7
+    lib.kb_sa_bwd_workspace_bytes.restype = C.c_uint64
     lib.kb_softmax_fwd.argtypes = [C.POINTER(SoftmaxParams), C.c_void_p]
     for f in (lib.kb_sa_fwd, lib.kb_fa_fwd, lib.kb_sa_bwd, lib.kb_softmax_fwd):
         f.restype = C.c_int

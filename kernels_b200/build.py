@@ -35,7 +35,8 @@ NVCC_FLAGS = [
 ]
 
 # translation units whose presence switches on a kernel family in capi.cu
-FEATURE_DEFINES = {"sa_fwd_sm100.cu": "-DKB_HAVE_SM100", "sa_bwd_sm100.cu": "-DKB_HAVE_SM100_BWD"}
+FEATURE_DEFINES = {"sa_fwd_sm100.cu": "-DKB_HAVE_SM100", "sa_bwd_sm100.cu": "-DKB_HAVE_SM100_BWD",
+                   "sa_bwd_fused_sm100.cu": "-DKB_HAVE_SM100_BWD_FUSED"}
 
 
 def _nvcc() -> str:

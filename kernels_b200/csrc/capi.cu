@@ -109,11 +109,30 @@ int kb_sa_bwd(const kb_sa_bwd_params* p, void* stream) {
   cudaStream_t s = static_cast<cudaStream_t>(stream);
 #ifdef KB_HAVE_SM100_BWD
   if (kb::select_bwd_path(*p) == KB_PATH_SM100) {
+#ifdef KB_HAVE_SM100_BWD_FUSED
+    // scores evaluated once when the caller brought the dS scratch; "unsupported" = nothing launched
+    if (p->ds_ws && !(p->flags & KB_FLAG_BWD_TWO_PASS)) {
+      const int rc = kb::sa_bwd_fused_sm100(*p, c, back, s);
+      if (rc != KB_ERR_UNSUPPORTED) return rc;
+    }
+#endif
     const int rc = kb::sa_bwd_sm100(*p, c, back, s);
     if (rc != KB_ERR_UNSUPPORTED) return rc;
   }
 #endif
   return kb::sa_bwd_generic(*p, c, back, s);
+}
+
+uint64_t kb_sa_bwd_workspace_bytes(int32_t B, int32_t H, int32_t T, int32_t D, int32_t dtype, int32_t context_size,
+                                   int32_t back_contexts) {
+#ifdef KB_HAVE_SM100_BWD_FUSED
+  if (B > 0 && H > 0 && T > 0 && context_size >= 1 && back_contexts >= 0 && kb::sm100_shape_ok(dtype, D, 0)) {
+    const int32_t c = kb_clamp_context(context_size, T);
+    return kb::sa_bwd_fused_workspace_bytes(B, H, T, c, kb_clamp_back(back_contexts, T, c));
+  }
+#endif
+  (void)B, (void)H, (void)T, (void)D, (void)dtype, (void)context_size, (void)back_contexts;
+  return 0;
 }
 
 int kb_softmax_fwd(const kb_softmax_params* p, void* stream) {

@@ -62,5 +62,7 @@ extern "C" int kb_sa_bwd_noalloc(const kb_sa_bwd_params* p, void* stream) {
   if (rc != KB_OK) return rc;
   kb_sa_bwd_params q = *p;
   q.delta_ws = scratch;  // whatever the caller put there is ignored
+  q.ds_ws = nullptr;  // the two-pass kernels need no scratch besides delta
+  q.ds_ws_bytes = 0;
   return kb_sa_bwd(&q, stream);
 }

@@ -26,6 +26,15 @@ from .. import _lib
 logger = logging.getLogger(__name__)
 
 _SUPPORTED_HEAD_DIMS = (16, 32, 64, 128, 256)
+# Largest dS scratch the backward op will allocate for the single-evaluation kernels.
+_MAX_DS_SCRATCH_BYTES = 48 << 30
+
+
+def _free_bytes(device) -> int:
+    """Device memory a new allocation can draw on: free in the driver plus cached by torch."""
+    free, _total = torch.cuda.mem_get_info(device)
+    return free + torch.cuda.memory_reserved(device) - torch.cuda.memory_allocated(device)
+
 
 
 def _flags(prescale_qk: bool, precision: str) -> int:
@@ -139,10 +148,14 @@ def attention_backward_adapter(
 ) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
     """Backward op body: ``(dQ, dK, dV)`` through ``kb_sa_bwd``.
 
-    ``delta = rowsum(O * dO)`` is produced inside the dQ pass; its ``[B, H, T]`` fp32 scratch
-    is allocated here and handed to the library (reference: kernel.py:1363-1442 runs it as
-    a separate launch).  ``do`` may arrive in another dtype or with any strides
-    (``tests/test_streaming_attention.py:98-112``): it is cast to ``q``'s dtype first.
+    Scratch is allocated here and handed to the library: ``delta = rowsum(O * dO)`` as
+    ``[B, H, T]`` fp32 (reference: kernel.py:1380) and, for the tcgen05 backward that evaluates
+    the scores once, room for the 16-bit dS tiles (``kb_sa_bwd_workspace_bytes``; it grows with
+    ``(back_contexts + 1) * context_size``).  When that room exceeds ``_MAX_DS_SCRATCH_BYTES`` or
+    a quarter of the device memory that is free, it is withheld and the library runs its two-pass
+    kernels, which need none.  ``do`` may arrive in another dtype or with any strides
+    (``tests/test_streaming_attention.py:98-112``): it is cast to
+    ``q``'s dtype first.
     """
     _check_inputs(q, k, v, lens, context_size, back_contexts, sm_scale)
     B, H, T, D = q.shape
@@ -166,12 +179,20 @@ def attention_backward_adapter(
     delta = torch.empty((B, H, T), dtype=torch.float32, device=q.device)
 
     lib = _lib.load()
+    ds_ws = None
+    if q.numel():
+        ws_bytes = int(lib.kb_sa_bwd_workspace_bytes(
+            B, H, T, D, _lib.dtype_code(q.dtype), _clamp_i32(context_size), _clamp_i32(back_contexts)))
+        if 0 < ws_bytes <= _MAX_DS_SCRATCH_BYTES and ws_bytes <= _free_bytes(q.device) // 4:
+            ds_ws = torch.empty(ws_bytes, dtype=torch.uint8, device=q.device)
     lens_keep, lens_ptr, lens_stride = _lens_arg(lens, q.device)
     p = _lib.SaBwdParams()
     p.q, p.k, p.v, p.o, p.d_o = (_lib.tensor4(t) for t in (q, k, v, o, do))
     p.lse = lse.data_ptr()
     p.dq, p.dk, p.dv = DQ.data_ptr(), DK.data_ptr(), DV.data_ptr()
     p.delta_ws = delta.data_ptr()
+    p.ds_ws = ds_ws.data_ptr() if ds_ws is not None else None
+    p.ds_ws_bytes = ds_ws.numel() if ds_ws is not None else 0
     p.lens, p.lens_stride = lens_ptr, lens_stride
     p.B, p.H, p.T, p.D = B, H, T, D
     p.dtype = _lib.dtype_code(q.dtype)

@@ -148,3 +148,35 @@ def test_operator_schemas_keep_reference_argument_order():
         "prescale_qk", "precision"]
     fa = torch.ops.alexdremov_flash_attention.forward.default._schema
     assert [a.name for a in fa.arguments] == ["q", "k", "v", "lens", "sm_scale", "autotune", "prescale"]
+
+
+def test_forward_and_backward_schedules_name_the_same_tile_pairs():
+    """The single-evaluation backward saves one dS tile per (key tile, query tile) pair of the
+    TRANSPOSED schedule and its dQ kernel reads them by the FORWARD schedule, at slot
+    ``query tile - first query tile of the key tile``: both schedules must list the same pairs."""
+    import random
+
+    rng = random.Random(7)
+    for _ in range(1500):
+        T = rng.choice([1, 5, 127, 128, 129, 300, 640, 777, 1000, 2048])
+        c = rng.choice([1, 3, 10, 32, 48, 64, 100, 128, 129, 256, 300, 10000])
+        back = rng.choice([0, 1, 2, 3, 5, 8, 10000])
+        L = rng.choice([T, max(1, T // 2), rng.randint(0, T), T + 1])
+        fwd, bwd = _lib.plan(T, L, c, back, 128, 128)
+        pairs_f = {(i, j) for i, (b, e) in enumerate(fwd) for j in range(b, e)}
+        pairs_b = {(i, j) for j, (b, e) in enumerate(bwd) for i in range(b, e)}
+        assert pairs_f == pairs_b, (T, c, back, L)
+
+
+def test_backward_workspace_size():
+    lib = _lib.load()
+    # bf16 B=4 H=32 T=16384 D=128 context 256 back 2: every 128-key tile meets at most 6 query tiles
+    assert lib.kb_sa_bwd_workspace_bytes(4, 32, 16384, 128, _lib.KB_BF16, 256, 2) == 4 * 32 * 128 * 6 * 32768
+    # the slot count is the widest row of the transposed schedule
+    for T, c, back in [(700, 48, 3), (1000, 64, 8), (130, 128, 1), (2048, 10000, 0), (16, 10, 5)]:
+        _, bwd = _lib.plan(T, T, c, back, 128, 128)
+        w = max(e - b for b, e in bwd)
+        assert lib.kb_sa_bwd_workspace_bytes(2, 3, T, 64, _lib.KB_F16, c, back) == 2 * 3 * len(bwd) * w * 32768
+    # no single-evaluation kernel for fp32 or other head dims: no scratch wanted
+    assert lib.kb_sa_bwd_workspace_bytes(2, 3, 700, 64, _lib.KB_F32, 48, 3) == 0
+    assert lib.kb_sa_bwd_workspace_bytes(2, 3, 700, 32, _lib.KB_F16, 48, 3) == 0

@@ -204,6 +204,64 @@ def test_golden_fixtures(golden):
         torch.testing.assert_close(lse.cpu()[valid], torch.from_numpy(cse["ker_lse"])[valid], atol=2e-5, rtol=0)
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16], ids=str)
+@pytest.mark.parametrize("D", [64, 128])
+def test_two_pass_backward_when_scratch_is_withheld(dtype, D, monkeypatch):
+    """Without room for the dS tiles the library runs its two-pass tcgen05 kernels: same parity bar."""
+    from kernels_b200.streaming_attention import kernel as K
+
+    monkeypatch.setattr(K, "_MAX_DS_SCRATCH_BYTES", 0)
+    for (B, H, T, c, back) in [(2, 2, 700, 48, 3), (1, 1, 2048, 256, 2), (1, 2, 1000, 64, 8)]:
+        _run_case(B, H, T, D, c, back, dtype, "none" if B == 1 else "tricky", False)
+
+
+@pytest.mark.parametrize("dtype,D", [(torch.bfloat16, 128), (torch.float16, 64)], ids=str)
+def test_single_evaluation_and_two_pass_backward_agree_bitwise(dtype, D):
+    """Both tcgen05 backward families add the same products in the same order (key tiles ascending
+    for dQ, query tiles ascending for dK / dV), so they must agree to the bit, through the C ABI."""
+    import ctypes
+
+    from kernels_b200 import _lib
+
+    lib = _lib.load()
+    _api()
+    torch.manual_seed(11)
+    for (B, H, T, c, back, lens) in [(2, 3, 1000, 256, 2, [1000, 517]), (2, 2, 700, 48, 3, [700, 333]),
+                                     (1, 2, 300, 10, 5, [299]), (3, 5, 4096, 128, 4, [4096, 100, 2500])]:
+        q, k, v, do = (torch.randn(B, H, T, D, device="cuda").to(dtype) for _ in range(4))
+        lens_t = torch.tensor(lens, dtype=torch.int32, device="cuda")
+        o, lse = torch.ops.alexdremov_streaming_attention.forward(q, k, v, lens_t, c, back, D ** -0.5, False, True,
+                                                                  False, "ieee")
+        results = []
+        for single in (False, True):
+            outs = [torch.full_like(q, float("nan")) for _ in range(3)]
+            delta = torch.empty(B, H, T, dtype=torch.float32, device="cuda")
+            p = _lib.SaBwdParams()
+            p.q, p.k, p.v, p.o, p.d_o = (_lib.tensor4(t) for t in (q, k, v, o, do))
+            p.lse, p.delta_ws = lse.data_ptr(), delta.data_ptr()
+            p.dq, p.dk, p.dv = (t.data_ptr() for t in outs)
+            ws = None
+            if single:
+                nb = int(lib.kb_sa_bwd_workspace_bytes(B, H, T, D, _lib.dtype_code(dtype), c, back))
+                assert nb > 0
+                ws = torch.empty(nb, dtype=torch.uint8, device="cuda")
+                p.ds_ws, p.ds_ws_bytes = ws.data_ptr(), nb
+            p.lens, p.lens_stride = lens_t.data_ptr(), 1
+            p.B, p.H, p.T, p.D = B, H, T, D
+            p.dtype = _lib.dtype_code(dtype)
+            p.context_size, p.back_contexts, p.sm_scale = c, back, float(D ** -0.5)
+            p.status = _lib.status_words().data_ptr()
+            n0 = _lib.launch_count()
+            _lib.check(lib.kb_sa_bwd(ctypes.byref(p), torch.cuda.current_stream().cuda_stream), "kb_sa_bwd")
+            torch.cuda.synchronize()
+            _lib.check_device_status()
+            assert _lib.launch_count() - n0 == (3 if single else 2)  # delta + main + dq  vs  dq pass + dk/dv pass
+            results.append(outs)
+        for name, a_, b_ in zip(("dq", "dk", "dv"), *results):
+            assert torch.isfinite(b_.float()).all(), name
+            assert torch.equal(a_, b_), (name, B, H, T, c, back)
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=str)
 def test_run_twice_is_bitwise_identical(dtype):
     """No atomics anywhere on the path: two runs give the same bits."""
