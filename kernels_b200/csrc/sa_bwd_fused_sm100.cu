@@ -72,6 +72,7 @@ constexpr int kThreads = 512;
 constexpr int kComputeThreads = 256, kEpiThreads = 128;
 constexpr int kEpiWarp0 = 8, kProducerWarp = 12, kMmaWarp = 13, kSpillWarp = 14;
 constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kRelaxedNs = 0;  // poll interval of the roles off the critical chain (no gain measured from sleeping)
 constexpr uint32_t kColS = 0, kColDP = 128, kColDV = 256, kColDK = 384;
 // register budgets after the warpgroups have traded (launch budget: 128 per thread)
 constexpr int kRegsCompute = 176, kRegsEpi = 104, kRegsOther = 56;
@@ -88,6 +89,7 @@ struct FusedArgs {
   const int32_t* lens;
   int64_t lens_stride;
   int32_t B, H, T, c, back, W;
+  KbFastDiv fd_tiles, fd_H, fd_c;  // division by ceil(T / 128), H and c
   float scale_log2, sm_scale;
   int32_t* status;
 };
@@ -139,22 +141,24 @@ struct Cursor {
   __device__ __forceinline__ bool last() const { return t == tiles() - 1; }
 };
 
-__device__ __forceinline__ Item decode_item(const FusedArgs& a, int item, int n_ktiles) {
+// `prev` is the item decoded before (b = -1: none): consecutive items mostly share the batch index
+// and with it the sequence length, which saves the global load.
+__device__ __forceinline__ Item decode_item(const FusedArgs& a, int item, int n_ktiles, const Item& prev) {
   Item it;
-  const int bh = item / n_ktiles;
+  const int bh = kb_fastdiv(item, a.fd_tiles);
   it.kt = item - bh * n_ktiles;
-  it.b = bh / a.H;
+  it.b = kb_fastdiv(bh, a.fd_H);
   it.h = bh - it.b * a.H;
   it.k0 = it.kt * kBK;
-  it.len = a.lens ? kb_clamp_len(a.lens[(int64_t)it.b * a.lens_stride], a.T) : a.T;
-  it.qr = kb_bwd_q_range(it.k0, kBQ, kBK, it.len, a.c, a.back);
+  it.len = !a.lens ? a.T : (it.b == prev.b ? prev.len : kb_clamp_len(a.lens[(int64_t)it.b * a.lens_stride], a.T));
+  it.qr = kb_bwd_q_range_fd(it.k0, kBQ, kBK, it.len, a.c, a.back, a.fd_c);
   return it;
 }
 // first live item at or after `item` (stride gridDim.x)
 __device__ __forceinline__ void seek_live(const FusedArgs& a, Cursor& c, int n_items, int n_ktiles) {
   c.valid = false;
   for (; c.item < n_items; c.item += gridDim.x) {
-    c.it = decode_item(a, c.item, n_ktiles);
+    c.it = decode_item(a, c.item, n_ktiles, c.it);
     if (c.it.qr.begin < c.it.qr.end) {
       c.valid = true;
       return;
@@ -165,6 +169,7 @@ __device__ __forceinline__ Cursor cursor_first(const FusedArgs& a, int n_items, 
   Cursor c;
   c.item = blockIdx.x;
   c.n = c.g = c.t = 0;
+  c.it.b = -1;
   seek_live(a, c, n_items, n_ktiles);
   return c;
 }
@@ -261,7 +266,7 @@ sa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
           if (c.t == 0) {
             const int ks = n & 1;
             // the buffer held K(n - 2), then staged that item's dV / dK on their way out
-            if (n >= 2) ok = mbar_wait(&sm.k_free[ks], ((n >> 1) - 1) & 1, ctx, kWKFree);
+            if (n >= 2) ok = mbar_wait<kRelaxedNs>(&sm.k_free[ks], ((n >> 1) - 1) & 1, ctx, kWKFree);
             if (ok) {
               mbar_expect_tx(&sm.k_full[ks], kTileBytes);
 #pragma unroll
@@ -269,7 +274,7 @@ sa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
                 tma_load_4d(sm.k[ks] + p * kPanelBytes, &tm_k, &sm.k_full[ks], p * 64, c.it.k0, c.it.h, c.it.b);
             }
           }
-          if (ok && g >= 2) ok = mbar_wait(&sm.q_empty[g & 1], ((g >> 1) - 1) & 1, ctx, kWQEmpty);
+          if (ok && g >= 2) ok = mbar_wait<kRelaxedNs>(&sm.q_empty[g & 1], ((g >> 1) - 1) & 1, ctx, kWQEmpty);
           if (ok) {
             mbar_expect_tx(&sm.q_full[g & 1], kTileBytes);
 #pragma unroll
@@ -278,7 +283,7 @@ sa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
           }
           KB_FTR(0, g, 1);
           if (ok && c.t == 0) {
-            if (n >= 1) ok = mbar_wait(&sm.v_empty, (n - 1) & 1, ctx, kWVEmpty);
+            if (n >= 1) ok = mbar_wait<kRelaxedNs>(&sm.v_empty, (n - 1) & 1, ctx, kWVEmpty);
             if (ok) {
               mbar_expect_tx(&sm.v_full, kTileBytes);
 #pragma unroll
@@ -286,7 +291,7 @@ sa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
                 tma_load_4d(sm.v + p * kPanelBytes, &tm_v, &sm.v_full, p * 64, c.it.k0, c.it.h, c.it.b);
             }
           }
-          if (ok && g >= 1) ok = mbar_wait(&sm.do_empty, (g - 1) & 1, ctx, kWDoEmpty);
+          if (ok && g >= 1) ok = mbar_wait<kRelaxedNs>(&sm.do_empty, (g - 1) & 1, ctx, kWDoEmpty);
           if (ok) {
             mbar_expect_tx(&sm.do_full, kTileBytes);
 #pragma unroll
@@ -297,7 +302,7 @@ sa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
         }
         // lse and delta of the tile's query rows, two slots deep: slot g & 1 was last read while
         // dS(g - 2) was formed
-        if (ok && g >= 2) ok = mbar_wait(&sm.ds_ready[g & 1], ((g >> 1) - 1) & 1, ctx, kWStatsSlot);
+        if (ok && g >= 2) ok = mbar_wait<kRelaxedNs>(&sm.ds_ready[g & 1], ((g >> 1) - 1) & 1, ctx, kWStatsSlot);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         const int64_t bh = (int64_t)c.it.b * a.H + c.it.h;
@@ -392,7 +397,7 @@ sa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
     } else if (warp == kSpillWarp && lane == 0) {
       // ------------------------------ dS tiles to the scratch buffer ------------------------------
       for (Cursor c = cursor_first(a, n_items, n_ktiles); c.valid; cursor_next(a, c, n_items, n_ktiles)) {
-        if (!mbar_wait(&sm.ds_ready[c.g & 1], (c.g >> 1) & 1, ctx, kWSpill)) break;
+        if (!mbar_wait<kRelaxedNs>(&sm.ds_ready[c.g & 1], (c.g >> 1) & 1, ctx, kWSpill)) break;
         bulk_store(ds_slot(a, c.it.b, c.it.h, c.it.kt, n_ktiles, c.t), sm.ds, kDsTileBytes);
         tma_store_commit();
         tma_store_wait_read();
@@ -418,7 +423,7 @@ sa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
         const int xi = c.it.k0 + row;
         lo = hi = 0;
         if (xi < c.it.len) {
-          const int xc = xi / a.c;
+          const int xc = kb_fastdiv(xi, a.fd_c);
           lo = xc * a.c;
           const int64_t h64 = (int64_t)(xc + a.back + 1) * a.c;
           hi = h64 < c.it.len ? (int)h64 : c.it.len;
@@ -513,8 +518,10 @@ sa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
     const uint32_t t_lane = tmem + ((uint32_t)((warp & 3) * 32) << 16);
     int n = 0;
     bool ok = true;
+    Item it;
+    it.b = -1;
     for (int item = blockIdx.x; ok && item < n_items; item += gridDim.x) {
-      const Item it = decode_item(a, item, n_ktiles);
+      it = decode_item(a, item, n_ktiles, it);
       const int64_t bh = (int64_t)it.b * a.H + it.h;
       const int kr = it.k0 + row;
       if (it.qr.begin >= it.qr.end) {
@@ -531,7 +538,7 @@ sa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
         continue;
       }
       // all four warps must take the same exit: they meet at named barriers below
-      ok = named_barrier_and(1, kEpiThreads, mbar_wait(&sm.acc_done, n & 1, ctx, kWAccDone));
+      ok = named_barrier_and(1, kEpiThreads, mbar_wait<kRelaxedNs>(&sm.acc_done, n & 1, ctx, kWAccDone));
       if (!ok) break;
       if (etid == 0) KB_FTR(3, n, 0);
       tc_fence_after();
@@ -678,14 +685,14 @@ struct DqItem {
   int b, h, qt, len;
   KbTileRange kr;  // key tiles [begin, end) the query tile visits: the forward schedule
 };
-__device__ __forceinline__ DqItem decode_dq_item(const FusedArgs& a, int item, int n_qtiles) {
+__device__ __forceinline__ DqItem decode_dq_item(const FusedArgs& a, int item, int n_qtiles, const DqItem& prev) {
   DqItem it;
-  const int bh = item / n_qtiles;
+  const int bh = kb_fastdiv(item, a.fd_tiles);
   it.qt = item - bh * n_qtiles;
-  it.b = bh / a.H;
+  it.b = kb_fastdiv(bh, a.fd_H);
   it.h = bh - it.b * a.H;
-  it.len = a.lens ? kb_clamp_len(a.lens[(int64_t)it.b * a.lens_stride], a.T) : a.T;
-  it.kr = kb_fwd_kv_range(it.qt * kBQ, kBQ, kBK, it.len, a.c, a.back);
+  it.len = !a.lens ? a.T : (it.b == prev.b ? prev.len : kb_clamp_len(a.lens[(int64_t)it.b * a.lens_stride], a.T));
+  it.kr = kb_fwd_kv_range_fd(it.qt * kBQ, kBQ, kBK, it.len, a.c, a.back, a.fd_c);
   return it;
 }
 
@@ -733,13 +740,15 @@ sa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
       prefetch_tensormap(&tm_k);
       int u = 0;
       bool ok = true;
+      DqItem it;
+      it.b = -1;
       for (int item = blockIdx.x; ok && item < n_items; item += gridDim.x) {
-        const DqItem it = decode_dq_item(a, item, n_tiles_t);
+        it = decode_dq_item(a, item, n_tiles_t, it);
         for (int j = it.kr.begin; j < it.kr.end; ++j, ++u) {
           const int s = u % kDqStages;
-          if (u >= kDqStages && !mbar_wait(&sm.empty[s], ((u / kDqStages) - 1) & 1, ctx, kWDqEmpty)) { ok = false; break; }
+          if (u >= kDqStages && !mbar_wait<kRelaxedNs>(&sm.empty[s], ((u / kDqStages) - 1) & 1, ctx, kWDqEmpty)) { ok = false; break; }
           // the slot this query tile has in key tile j's list: both schedules name the same pairs
-          const KbTileRange qr = kb_bwd_q_range(j * kBK, kBQ, kBK, it.len, a.c, a.back);
+          const KbTileRange qr = kb_bwd_q_range_fd(j * kBK, kBQ, kBK, it.len, a.c, a.back, a.fd_c);
           mbar_expect_tx(&sm.full[s], kDsTileBytes + kTileBytes);
           bulk_load(sm.ds[s], ds_slot(a, it.b, it.h, j, n_tiles_t, it.qt - qr.begin), kDsTileBytes, &sm.full[s]);
 #pragma unroll
@@ -753,8 +762,10 @@ sa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
       constexpr uint32_t idesc = make_idesc(BF16, kBQ, D, true, true);  // A = dS read MN-major (rows = keys), B = K MN-major
       int u = 0, m = 0;
       bool ok = true;
+      DqItem it;
+      it.b = -1;
       for (int item = blockIdx.x; ok && item < n_items; item += gridDim.x) {
-        const DqItem it = decode_dq_item(a, item, n_tiles_t);
+        it = decode_dq_item(a, item, n_tiles_t, it);
         if (it.kr.begin >= it.kr.end) continue;
         const uint32_t acc = tmem + (m & 1) * 128;
         if (m >= 2 && !mbar_wait(&sm.acc_free[m & 1], ((m >> 1) - 1) & 1, ctx, kWDqAccFree)) break;
@@ -778,8 +789,10 @@ sa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
     const uint32_t t_lane = tmem + ((uint32_t)(warp * 32) << 16);
     int m = 0;
     bool ok = true;
+    DqItem it;
+    it.b = -1;
     for (int item = blockIdx.x; ok && item < n_items; item += gridDim.x) {
-      const DqItem it = decode_dq_item(a, item, n_tiles_t);
+      it = decode_dq_item(a, item, n_tiles_t, it);
       const int qi = it.qt * kBQ + row;
       if (it.kr.begin >= it.kr.end) {
         // the whole query tile lies in the padding: its gradient is zero (rare; plain stores)
@@ -791,7 +804,7 @@ sa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
         continue;
       }
       // all four warps must take the same exit: they meet at named barriers below
-      ok = named_barrier_and(1, 128, mbar_wait(&sm.acc_done[m & 1], (m >> 1) & 1, ctx, kWDqAccDone));
+      ok = named_barrier_and(1, 128, mbar_wait<kRelaxedNs>(&sm.acc_done[m & 1], (m >> 1) & 1, ctx, kWDqAccDone));
       if (!ok) break;
       tc_fence_after();
 #pragma unroll
@@ -894,6 +907,9 @@ int launch_fused(const kb_sa_bwd_params& p, int32_t c, int32_t back, cudaStream_
   fa.c = c;
   fa.back = back;
   fa.W = fused_slots(p.T, c, back);
+  fa.fd_tiles = kb_fastdiv_make(n_tiles);
+  fa.fd_H = kb_fastdiv_make(p.H);
+  fa.fd_c = kb_fastdiv_make(c);
   fa.scale_log2 = p.sm_scale * kLog2e;
   fa.sm_scale = p.sm_scale;
   fa.status = p.status;

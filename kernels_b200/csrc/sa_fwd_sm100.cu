@@ -60,6 +60,7 @@ struct FwdArgs {
   const int32_t* lens;
   int64_t lens_stride;
   int32_t B, H, T, c, back;
+  KbFastDiv fd_qblocks, fd_H, fd_c;  // division by ceil(T / 256), H and c
   float scale_log2;
   int32_t* status;
 };
@@ -161,14 +162,14 @@ sa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   };
   auto decode = [&](int item) {
     Item it;
-    const int qb = item % n_qblocks, bh = item / n_qblocks;
-    it.b = bh / a.H;
+    const int bh = kb_fastdiv(item, a.fd_qblocks), qb = item - bh * n_qblocks;
+    it.b = kb_fastdiv(bh, a.fd_H);
     it.h = bh - it.b * a.H;
     it.q0 = qb * (kBM * kQTiles);
     it.len = a.lens ? kb_clamp_len(a.lens[(int64_t)it.b * a.lens_stride], T) : T;
 #pragma unroll
     for (int x = 0; x < kQTiles; ++x) {
-      it.kr[x] = kb_fwd_kv_range(it.q0 + x * kBM, kBM, kBN, it.len, a.c, a.back);
+      it.kr[x] = kb_fwd_kv_range_fd(it.q0 + x * kBM, kBM, kBN, it.len, a.c, a.back, a.fd_c);
       it.act[x] = it.kr[x].begin < it.kr[x].end;
     }
     it.u_begin = it.act[0] ? it.kr[0].begin : it.kr[1].begin;
@@ -336,7 +337,7 @@ sa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       const int n_tiles = it.kr[x].end - it.kr[x].begin;
       int lo = 0, hi = 0;
       if (qi < it.len) {
-        const int qc = qi / a.c;
+        const int qc = kb_fastdiv(qi, a.fd_c);
         lo = kb_max_i32(0, qc - a.back) * a.c;
         const int64_t h64 = (int64_t)(qc + 1) * a.c;
         hi = h64 < it.len ? (int)h64 : it.len;
@@ -430,6 +431,9 @@ int launch(const kb_sa_fwd_params& p, int32_t c, int32_t back, cudaStream_t s) {
   a.T = p.T;
   a.c = c;
   a.back = back;
+  a.fd_qblocks = kb_fastdiv_make(kb_cdiv_i32(p.T, kBM * kQTiles));
+  a.fd_H = kb_fastdiv_make(p.H);
+  a.fd_c = kb_fastdiv_make(c);
   a.scale_log2 = p.sm_scale * kLog2e;
   a.status = p.status;
   const int64_t n_items = (int64_t)p.B * p.H * kb_cdiv_i32(p.T, kBM * kQTiles);

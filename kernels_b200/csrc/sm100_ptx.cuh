@@ -71,11 +71,16 @@ struct WaitCtx {
   int32_t* status;           // global / pinned host, may be null
 };
 
+// kSleepNs > 0: sleep that long between polls.  For roles that wait for a large part of a tile
+// or item and are not on the critical chain (epilogue, producer, scratch copy): every poll is a
+// shared-memory access that competes with the operand fetches of the MMAs.
+template <uint32_t kSleepNs = 0>
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const WaitCtx& ctx, int where) {
   if (mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = globaltimer_ns();
   uint32_t spins = 0;
   while (true) {
+    if (kSleepNs) __nanosleep(kSleepNs);
     if (mbar_try_wait(bar, parity)) return true;
     if ((++spins & 63u) == 0) {
       if (*ctx.abort_flag) return false;
