@@ -11,7 +11,8 @@ Prints ONE JSON line on rank 0:
 * ``e2e``       the same metric through the public Python API with HOST (pinned) buffers:
                 host->device copies of q, k, v, dO and device->host copies of O, dQ, dK, dV
                 are inside the timed region;
-* ``roofline``  the dominant kernel (dK/dV pass) against the measured bf16 tensor peak;
+* ``roofline``  the dominant kernel (the backward kernel that forms dK and dV) against the measured bf16
+                tensor peak;
 * ``cpu_baseline`` the CPU oracle (a port of the reference's torch masked-attention path)
                 timed on this machine's host cores on a bounded sample of the same workload.
 
@@ -56,10 +57,12 @@ WORKLOADS = {
 }
 TORCH_DTYPES = {"bf16": torch.bfloat16, "f16": torch.float16, "f32": torch.float32}
 
-# dram__bytes_read.sum + dram__bytes_write.sum of the dK/dV pass per (batch, head) slice of T=16384, D=128,
-# c=256, back=2, lens=T, from the ncu capture of workload `prof` (32 slices, 782 MB; traffic is proportional to the
-# number of slices: every slice reads Q, K, V, dO once and writes dK, dV once).
-NCU_TRAFFIC_PER_SLICE = {"bwd_dkdv_pass": {"cfg3": 782e6 / 32, "prof": 782e6 / 32}}
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant backward kernel, per (batch, head)
+# slice of T=16384, D=128, c=256, back=2, lens=T, from ncu captures of workload `prof` (32 slices; see profiles/).
+# Traffic is proportional to the number of slices: every slice reads Q, K, V, dO once and writes dK, dV once
+# (two-pass dK/dV pass: 782 MB), plus, in the single-evaluation main kernel, its 16-bit dS tiles (1 640 MB).
+NCU_TRAFFIC_PER_SLICE = {"bwd_dkdv_pass": {"cfg3": 782e6 / 32, "prof": 782e6 / 32},
+                         "bwd_main": {"cfg3": 1640e6 / 32, "prof": 1640e6 / 32}}
 
 
 def _peaks():
@@ -341,22 +344,49 @@ def run_own(args, w):
             for i, name in enumerate(kernel_names)}
 
     # ---- end to end through the public API with host buffers ----
-    qd, kd, vd = (torch.empty_like(q).requires_grad_() for _ in range(3))
-    dod = torch.empty_like(q)
-    ho, hdq, hdk, hdv = (torch.empty(q.shape, dtype=dtype, pin_memory=True) for _ in range(4))
+    # The batch is cut into chunks (one batch element each); chunk i's host->device copies, chunk i-1's
+    # forward + backward and chunk i-2's device->host copies run on three streams, so the two PCIe
+    # directions and the GPU work overlap.  Every chunk goes through the public streaming_attention().
+    n_chunks = B
+    s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+    host_in = [[t[i:i + 1] for t in (hq, hk, hv, hdo)] for i in range(n_chunks)]
+    host_out = [[torch.empty((1,) + tuple(q.shape[1:]), dtype=dtype, pin_memory=True) for _ in range(4)]
+                for _ in range(n_chunks)]
+    dev_in = [[torch.empty((1,) + tuple(q.shape[1:]), dtype=dtype, device=dev) for _ in range(4)] for _ in range(n_chunks)]
+    for bufs in dev_in:
+        for t_ in bufs[:3]:
+            t_.requires_grad_()
+    lens_chunks = [None if lens_d is None else lens_d[i:i + 1] for i in range(n_chunks)]
+    computed = [None] * n_chunks  # per chunk: event after its last forward + backward (readers of dev_in[i])
 
     def e2e_step():
-        with torch.no_grad():
-            for dst, src in ((qd, hq), (kd, hk), (vd, hv), (dod, hdo)):
-                dst.copy_(src, non_blocking=True)
-        for t_ in (qd, kd, vd):
-            t_.grad = None
-        out = streaming_attention(qd, kd, vd, lens_d, w["c"], w["back"])
-        out.backward(dod)
-        ho.copy_(out.detach(), non_blocking=True)
-        hdq.copy_(qd.grad, non_blocking=True)
-        hdk.copy_(kd.grad, non_blocking=True)
-        hdv.copy_(vd.grad, non_blocking=True)
+        done = []
+        for i in range(n_chunks):
+            qd, kd, vd, dod = dev_in[i]
+            ev_in = torch.cuda.Event()
+            with torch.cuda.stream(s_in), torch.no_grad():
+                if computed[i] is not None:
+                    s_in.wait_event(computed[i])  # last step's kernels have read the chunk's buffers
+                for dst, src in zip((qd, kd, vd, dod), host_in[i]):
+                    dst.copy_(src, non_blocking=True)
+                ev_in.record(s_in)
+            stream.wait_event(ev_in)
+            for t_ in (qd, kd, vd):
+                t_.grad = None
+            out = streaming_attention(qd, kd, vd, lens_chunks[i], w["c"], w["back"])
+            out.backward(dod)
+            ev_c = torch.cuda.Event()
+            ev_c.record(stream)
+            computed[i] = ev_c
+            results = (out.detach(), qd.grad, kd.grad, vd.grad)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(ev_c)
+                for dst, src in zip(host_out[i], results):
+                    src.record_stream(s_out)
+                    dst.copy_(src, non_blocking=True)
+            done.append(results)
+        stream.wait_stream(s_out)
+        stream.wait_stream(s_in)
 
     e2e_steps = 0 if args.no_e2e else max(1, min(args.steps, 10))
     for _ in range(3 if e2e_steps else 0):

@@ -264,6 +264,18 @@ sa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
           KB_FTR(0, g, 0);
           // order of issue = order of need: S wants K and Q, dP (issued a tile later) wants V and dO
           if (c.t == 0) {
+            // K and V of an item are read by this CTA only, so they always come from DRAM: have the
+            // next item's tiles brought into L2 a whole item ahead of their loads
+            Cursor nx = c;
+            nx.t = nx.tiles() - 1;
+            cursor_next(a, nx, n_items, n_ktiles);
+            if (nx.valid) {
+#pragma unroll
+              for (int p = 0; p < kPanels; ++p) {
+                tma_prefetch_l2_4d(&tm_k, p * 64, nx.it.k0, nx.it.h, nx.it.b);
+                tma_prefetch_l2_4d(&tm_v, p * 64, nx.it.k0, nx.it.h, nx.it.b);
+              }
+            }
             const int ks = n & 1;
             // the buffer held K(n - 2), then staged that item's dV / dK on their way out
             if (n >= 2) ok = mbar_wait<kRelaxedNs>(&sm.k_free[ks], ((n >> 1) - 1) & 1, ctx, kWKFree);
