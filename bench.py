@@ -344,19 +344,23 @@ def run_own(args, w):
             for i, name in enumerate(kernel_names)}
 
     # ---- end to end through the public API with host buffers ----
-    # The batch is cut into chunks (one batch element each); chunk i's host->device copies, chunk i-1's
-    # forward + backward and chunk i-2's device->host copies run on three streams, so the two PCIe
+    # The batch is cut into chunks of at least ~128 MB of input; chunk i's host->device copies, chunk
+    # i-1's forward + backward and chunk i-2's device->host copies run on three streams, so the two PCIe
     # directions and the GPU work overlap.  Every chunk goes through the public streaming_attention().
-    n_chunks = B
+    in_bytes = 4 * q.numel() * q.element_size()
+    n_chunks = max(1, min(B, in_bytes // (128 << 20)))
+    while B % n_chunks:
+        n_chunks -= 1
+    cb = B // n_chunks  # batch elements per chunk
     s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
-    host_in = [[t[i:i + 1] for t in (hq, hk, hv, hdo)] for i in range(n_chunks)]
-    host_out = [[torch.empty((1,) + tuple(q.shape[1:]), dtype=dtype, pin_memory=True) for _ in range(4)]
+    host_in = [[t[i * cb:(i + 1) * cb] for t in (hq, hk, hv, hdo)] for i in range(n_chunks)]
+    host_out = [[torch.empty((cb,) + tuple(q.shape[1:]), dtype=dtype, pin_memory=True) for _ in range(4)]
                 for _ in range(n_chunks)]
-    dev_in = [[torch.empty((1,) + tuple(q.shape[1:]), dtype=dtype, device=dev) for _ in range(4)] for _ in range(n_chunks)]
+    dev_in = [[torch.empty((cb,) + tuple(q.shape[1:]), dtype=dtype, device=dev) for _ in range(4)] for _ in range(n_chunks)]
     for bufs in dev_in:
         for t_ in bufs[:3]:
             t_.requires_grad_()
-    lens_chunks = [None if lens_d is None else lens_d[i:i + 1] for i in range(n_chunks)]
+    lens_chunks = [None if lens_d is None else lens_d[i * cb:(i + 1) * cb] for i in range(n_chunks)]
     computed = [None] * n_chunks  # per chunk: event after its last forward + backward (readers of dev_in[i])
 
     def e2e_step():
@@ -382,9 +386,10 @@ def run_own(args, w):
             with torch.cuda.stream(s_out):
                 s_out.wait_event(ev_c)
                 for dst, src in zip(host_out[i], results):
-                    src.record_stream(s_out)
                     dst.copy_(src, non_blocking=True)
-            done.append(results)
+            done.append(results)  # keeps the device results allocated until the copies are ordered below
+        # the launching stream joins the copy streams: work queued after this step (which may reuse the
+        # results' memory once `done` is dropped) runs after this step's device->host copies
         stream.wait_stream(s_out)
         stream.wait_stream(s_in)
 

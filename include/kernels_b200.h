@@ -197,7 +197,8 @@ KB_API int kb_sa_plan(int32_t T, int32_t seq_len, int32_t context_size, int32_t 
  * Host-only: the committed tile table that replaces the reference's per-GPU config
  * tables and autotuner (src/streaming_attention/kernel.py:17-192, 1133-1267).
  * Writes the kernel family (KB_PATH_*) and its q/kv tile sizes and pipeline depth for
- * the forward (`which` = 0), the dQ pass (1) or the dK/dV pass (2).
+ * the forward (`which` = 0), the two-pass backward's dQ pass (1) and dK/dV pass (2), the
+ * single-evaluation backward's main kernel (3) and dQ kernel (4).
  */
 KB_API int kb_sa_tile_config(int32_t dtype, int32_t D, int32_t context_size, uint32_t flags, int32_t unit_inner_stride,
                       int32_t which, int32_t* path, int32_t* tile_q, int32_t* tile_k, int32_t* stages);

@@ -161,7 +161,8 @@ def plan(T: int, seq_len: int, context_size: int, back_contexts: int, tile_q: in
 
 
 def tile_config(dtype: torch.dtype, D: int, context_size: int, which: int = 0, flags: int = 0, unit_inner_stride=True):
-    """Committed tile table: ``dict(path, tile_q, tile_k, stages)`` for forward (0), dQ (1), dK/dV (2)."""
+    """Committed tile table: ``dict(path, tile_q, tile_k, stages)`` for forward (0), the two-pass backward's
+    dQ pass (1) and dK/dV pass (2), the single-evaluation backward's main kernel (3) and dQ kernel (4)."""
     lib = load()
     vals = [C.c_int32() for _ in range(4)]
     rc = lib.kb_sa_tile_config(dtype_code(dtype), D, context_size, flags, int(unit_inner_stride), which,

@@ -169,7 +169,7 @@ int kb_sa_tile_config(int32_t dtype, int32_t D, int32_t context_size, uint32_t f
                       int32_t which, int32_t* path, int32_t* tile_q, int32_t* tile_k, int32_t* stages) {
   (void)context_size;
   if (!kb::dtype_ok(dtype) || !kb::head_dim_ok(D)) return KB_ERR_UNSUPPORTED;
-  if (which < 0 || which > 2) return KB_ERR_BAD_ARGUMENT;
+  if (which < 0 || which > 4) return KB_ERR_BAD_ARGUMENT;
   int32_t pth = KB_PATH_GENERIC, tq = D <= 128 ? 64 : 32, tk = tq, st = 1;
 #ifdef KB_HAVE_SM100
   if (kb::sm100_shape_ok(dtype, D, flags) && unit_inner_stride) {
@@ -182,11 +182,20 @@ int kb_sa_tile_config(int32_t dtype, int32_t D, int32_t context_size, uint32_t f
       st = 3;
     }
 #ifdef KB_HAVE_SM100_BWD
-    if (which != 0) {
+    if (which == 1 || which == 2) {
       pth = KB_PATH_SM100;
       tq = 128;
       tk = 128;
       st = 3;
+    }
+#endif
+#ifdef KB_HAVE_SM100_BWD_FUSED
+    // single-evaluation backward: main kernel (Q ring 2 deep), dQ kernel (dS / K ring 3 deep)
+    if (which == 3 || which == 4) {
+      pth = KB_PATH_SM100;
+      tq = 128;
+      tk = 128;
+      st = which == 3 ? 2 : 3;
     }
 #endif
   }

@@ -89,6 +89,9 @@ def test_tile_table():
         for D in (64, 128):
             cfg = _lib.tile_config(dt, D, 256, which=0)
             assert cfg["tile_q"] % 16 == 0 and cfg["tile_k"] % 16 == 0 and cfg["stages"] >= 1
+            for which in (1, 2, 3, 4):  # both backward families are tcgen05 kernels on 128 x 128 tiles
+                cfg = _lib.tile_config(dt, D, 256, which=which)
+                assert cfg["path"] == _lib.KB_PATH_SM100 and (cfg["tile_q"], cfg["tile_k"]) == (128, 128)
     cfg = _lib.tile_config(torch.float32, 128, 256)
     assert cfg["path"] == _lib.KB_PATH_GENERIC
     cfg = _lib.tile_config(torch.float16, 64, 256, flags=_lib.KB_FLAG_FORCE_GENERIC)
