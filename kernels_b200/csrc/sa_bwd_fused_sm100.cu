@@ -114,7 +114,7 @@ struct alignas(1024) FusedSmem {
   alignas(16) float lse_s[2][kBQ];
   alignas(16) float delta_s[2][kBQ];
   uint64_t k_full[2], k_free[2], v_full, v_empty, q_full[2], q_empty[2], do_full, do_empty;
-  uint64_t s_ready, p_ready, dp_ready, ds_ready[2], ds_free, stats_full[2], acc_done, dv_free, dk_free;
+  uint64_t s_ready, p_ready, dp_ready, ds_ready[2], ds_free, stats_full[2], dv_done, dk_done, dv_free, dk_free;
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -225,7 +225,8 @@ sa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
     mbar_init(&sm.p_ready, kComputeThreads);
     mbar_init(&sm.dp_ready, 1);
     mbar_init(&sm.ds_free, 1);
-    mbar_init(&sm.acc_done, 1);
+    mbar_init(&sm.dv_done, 1);
+    mbar_init(&sm.dk_done, 1);
     mbar_init(&sm.dv_free, kEpiThreads);
     mbar_init(&sm.dk_free, kEpiThreads);
     sm.abort_flag = 0;
@@ -332,6 +333,13 @@ sa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
       constexpr uint32_t idesc_z = make_idesc(BF16, kBK, kBQ, false, false);  // S, dP
       constexpr uint32_t idesc_acc = make_idesc(BF16, kBK, D, false, true);   // dV, dK (A in TMEM)
       const uint32_t v_addr = smem_u32(sm.v), do_addr = smem_u32(sm.d_o);
+#ifdef KB_TRACE_FUSED
+      long long acc_t[12] = {0};
+      long long tl = clock64();
+#define KB_ACC(i) do { const long long tn_ = clock64(); acc_t[i] += tn_ - tl; tl = tn_; } while (0)
+#else
+#define KB_ACC(i) do { } while (0)
+#endif
 
       // The eight instructions of a matmul are issued from rolled loops on purpose: the MMA thread shares
       // its instruction cache with compute warps that run long unrolled loops, and a short issue path
@@ -340,6 +348,7 @@ sa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
       auto issue_s = [&](const Cursor& c) -> bool {
         if (c.t == 0 && !mbar_wait(&sm.k_full[c.n & 1], (c.n >> 1) & 1, ctx, kWKFull)) return false;
         if (!mbar_wait(&sm.q_full[c.g & 1], (c.g >> 1) & 1, ctx, kWQFull)) return false;
+        KB_ACC(9);  // waits for K, Q (counted apart from the issue of S)
         tc_fence_after();
         const uint32_t k_addr = smem_u32(sm.k[c.n & 1]), q_addr = smem_u32(sm.q[c.g & 1]);
 #pragma unroll 1
@@ -354,6 +363,7 @@ sa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
       auto issue_dp = [&](const Cursor& c) -> bool {
         if (c.t == 0 && !mbar_wait(&sm.v_full, c.n & 1, ctx, kWVFull)) return false;
         if (!mbar_wait(&sm.do_full, c.g & 1, ctx, kWDoFull)) return false;
+        KB_ACC(10);  // waits for V, dO (counted apart from the issue of dP)
         tc_fence_after();
 #pragma unroll 1
         for (int kk = 0; kk < D / 16; ++kk) {
@@ -378,39 +388,56 @@ sa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
 
       Cursor cur = cursor_first(a, n_items, n_ktiles);
       bool ok = cur.valid && issue_s(cur) && issue_dp(cur);
+      Cursor nxt = cur;
+      if (ok) cursor_next(a, nxt, n_items, n_ktiles);
+      KB_ACC(11);
       while (ok) {
-        Cursor nxt = cur;
-        cursor_next(a, nxt, n_items, n_ktiles);
         const int g = cur.g;
 
         const bool first = cur.t == 0;
         KB_FTR(1, g, 0);
         // dV(g) += P(g) dO(g)
+        KB_ACC(0);  // cursor
         if (!mbar_wait(&sm.p_ready, g & 1, ctx, kWPReady)) break;
+        KB_ACC(1);  // wait p_ready
         // the first MMAs of an item overwrite dV / dK: the epilogue warps must have read the old ones
         if (first && cur.n > 0 && !mbar_wait(&sm.dv_free, (cur.n - 1) & 1, ctx, kWAccFree)) break;
         KB_FTR(1, g, 1);
+        KB_ACC(2);  // wait dv_free
         tc_fence_after();
         issue_acc(kColDV, kColS, do_addr, first);
         mma_commit(&sm.do_empty);
+        if (cur.last()) mma_commit(&sm.dv_done);  // the epilogue warps start on dV while dK(last) still runs
         KB_FTR(1, g, 2);
+        KB_ACC(3);  // issue dV
         // S(g+1)
         if (nxt.valid && !issue_s(nxt)) break;
         KB_FTR(1, g, 3);
+        KB_ACC(4);  // S(g+1) incl. waits for K, Q
         // dK(g) += dS(g) Q(g)
         if (!mbar_wait(&sm.ds_ready[g & 1], (g >> 1) & 1, ctx, kWDsReady)) break;
+        KB_ACC(5);  // wait ds_ready
         if (first && cur.n > 0 && !mbar_wait(&sm.dk_free, (cur.n - 1) & 1, ctx, kWAccFree)) break;
+        KB_ACC(6);  // wait dk_free
         KB_FTR(1, g, 4);
         tc_fence_after();
         issue_acc(kColDK, kColDP, smem_u32(sm.q[g & 1]), first);
         mma_commit(&sm.q_empty[g & 1]);
-        if (cur.last()) mma_commit(&sm.acc_done);
+        if (cur.last()) mma_commit(&sm.dk_done);
         KB_FTR(1, g, 5);
+        KB_ACC(7);  // issue dK
         if (!nxt.valid) break;
         // dP(g+1)
         if (!issue_dp(nxt)) break;
+        KB_ACC(8);  // dP(g+1) incl. waits for V, dO
         cur = nxt;
+        cursor_next(a, nxt, n_items, n_ktiles);
+        KB_ACC(11);  // advancing the cursors
       }
+#ifdef KB_TRACE_FUSED
+      if (blockIdx.x == 60)
+        for (int i = 0; i < 12; ++i) g_ftrace[3][62][i % 8 + 0] = 0, g_ftrace[3][60 + i / 8][i % 8] = acc_t[i];
+#endif
     } else if (warp == kSpillWarp && lane == 0) {
       // ------------------------------ dS tiles to the scratch buffer ------------------------------
       for (Cursor c = cursor_first(a, n_items, n_ktiles); c.valid; cursor_next(a, c, n_items, n_ktiles)) {
@@ -554,15 +581,16 @@ sa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
         }
         continue;
       }
-      // all four warps must take the same exit: they meet at named barriers below
-      ok = named_barrier_and(1, kEpiThreads, mbar_wait<kRelaxedNs>(&sm.acc_done, n & 1, ctx, kWAccDone));
-      if (!ok) break;
-      if (etid == 0) KB_FTR(3, n, 0);
-      tc_fence_after();
       uint8_t* stage = sm.k[n & 1];
 #pragma unroll
       for (int which = 0; which < 2; ++which) {
         const float mul = which ? a.sm_scale : 1.f;
+        // dV is complete after the item's last dV MMA (every S that reads the K buffer ran before it),
+        // dK one matmul later.  All four warps must take the same exit: they meet at named barriers.
+        ok = named_barrier_and(1, kEpiThreads, mbar_wait<kRelaxedNs>(which ? &sm.dk_done : &sm.dv_done, n & 1, ctx, kWAccDone));
+        if (!ok) break;
+        if (etid == 0) KB_FTR(3, n, which);
+        tc_fence_after();
 #pragma unroll
         for (int cc = 0; cc < D / 32; ++cc) {
           uint32_t r[32];
@@ -596,7 +624,7 @@ sa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
         }
         named_barrier_sync(1, kEpiThreads);  // `stage` may be overwritten
       }
-      if (etid == 0) KB_FTR(3, n, 1);
+      if (!ok) break;
       ++n;
     }
     if (etid == 0) tma_store_wait_all();

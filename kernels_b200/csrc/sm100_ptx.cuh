@@ -61,38 +61,40 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Every wait in the kernels goes through this: it gives up after kWaitLimitNs, records where
-// in the status words and raises the CTA-wide abort flag, so a protocol bug or a lost copy
-// ends the kernel with an error code instead of hanging the GPU.
-constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s
+// Every wait in the kernels goes through this: it gives up after kWaitLimitSpins polls, records
+// where in the status words and raises the CTA-wide abort flag, so a protocol bug or a lost copy
+// ends the kernel with an error code instead of hanging the GPU.  A poll (try_wait) suspends the
+// thread for a hardware-defined time of the order of a microsecond at most, so the limit is reached
+// after a few seconds at the latest.  The wait is kept to a handful of instructions on purpose: it is
+// inlined at every wait site of every role, and the single-thread roles (MMA issue, TMA producer) run
+// out of an instruction cache they share with the compute warps' long unrolled loops.
+constexpr uint32_t kWaitLimitSpins = 1u << 22;
 
 struct WaitCtx {
   volatile int* abort_flag;  // shared memory
   int32_t* status;           // global / pinned host, may be null
 };
 
-// kSleepNs > 0: sleep that long between polls.  For roles that wait for a large part of a tile
-// or item and are not on the critical chain (epilogue, producer, scratch copy): every poll is a
-// shared-memory access that competes with the operand fetches of the MMAs.
+static __device__ __noinline__ bool mbar_give_up(volatile int* abort_flag, int32_t* status, int where) {
+  *abort_flag = 1;
+  if (status) {
+    atomicExch(status, KB_ERR_DEVICE_TIMEOUT);
+    atomicExch(status + 1, where);
+    atomicExch(status + 2, (int)blockIdx.x);
+  }
+  return false;
+}
+
+// kSleepNs > 0: sleep that long between polls (for roles far off the critical chain).
 template <uint32_t kSleepNs = 0>
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const WaitCtx& ctx, int where) {
   if (mbar_try_wait(bar, parity)) return true;
-  const uint64_t t0 = globaltimer_ns();
-  uint32_t spins = 0;
-  while (true) {
+  for (uint32_t spins = 1;; ++spins) {
     if (kSleepNs) __nanosleep(kSleepNs);
     if (mbar_try_wait(bar, parity)) return true;
-    if ((++spins & 63u) == 0) {
+    if ((spins & 63u) == 0) {
       if (*ctx.abort_flag) return false;
-      if (globaltimer_ns() - t0 > kWaitLimitNs) {
-        *ctx.abort_flag = 1;
-        if (ctx.status) {
-          atomicExch(ctx.status, KB_ERR_DEVICE_TIMEOUT);
-          atomicExch(ctx.status + 1, where);
-          atomicExch(ctx.status + 2, (int)blockIdx.x);
-        }
-        return false;
-      }
+      if (spins >= kWaitLimitSpins) return mbar_give_up(ctx.abort_flag, ctx.status, where);
     }
   }
 }
