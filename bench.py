@@ -60,9 +60,9 @@ TORCH_DTYPES = {"bf16": torch.bfloat16, "f16": torch.float16, "f32": torch.float
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant backward kernel, per (batch, head)
 # slice of T=16384, D=128, c=256, back=2, lens=T, from ncu captures of workload `prof` (32 slices; see profiles/).
 # Traffic is proportional to the number of slices: every slice reads Q, K, V, dO once and writes dK, dV once
-# (two-pass dK/dV pass: 782 MB), plus, in the single-evaluation main kernel, its 16-bit dS tiles (1 640 MB).
+# (two-pass dK/dV pass: 782 MB), plus, in the single-evaluation main kernel, its 16-bit dS tiles (1 624 MB).
 NCU_TRAFFIC_PER_SLICE = {"bwd_dkdv_pass": {"cfg3": 782e6 / 32, "prof": 782e6 / 32},
-                         "bwd_main": {"cfg3": 1640e6 / 32, "prof": 1640e6 / 32}}
+                         "bwd_main": {"cfg3": 1624e6 / 32, "prof": 1624e6 / 32}}
 
 
 def _peaks():
