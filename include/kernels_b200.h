@@ -91,6 +91,12 @@ typedef struct kb_sa_fwd_params {
   float sm_scale;
   uint32_t flags;
   int32_t* status; /* KB_STATUS_WORDS words, or NULL */
+  /* Shared key/value heads (grouped-query attention; an extension, the reference requires equal head
+   * counts, src/streaming_attention/kernel.py:1291).  0 or H: k and v have H heads.  Otherwise k and v are
+   * [B, H_kv, T, D], H a multiple of H_kv, and query head h reads key/value head h / (H / H_kv).  Only the
+   * tcgen05 kernels take H_kv != H; other calls return KB_ERR_UNSUPPORTED with nothing launched (the caller
+   * then repeats the K/V heads itself). */
+  int32_t H_kv;
 } kb_sa_fwd_params;
 
 KB_API int kb_sa_fwd(const kb_sa_fwd_params* p, void* stream);
@@ -129,6 +135,10 @@ typedef struct kb_sa_bwd_params {
   int32_t* status;
   void* ds_ws;          /* scratch of kb_sa_bwd_workspace_bytes() bytes, 16-byte aligned, or NULL */
   uint64_t ds_ws_bytes; /* its size; too small a scratch selects the two-pass kernels          */
+  /* Shared key/value heads, as in kb_sa_fwd_params: k, v, dk, dv are [B, H_kv, T, D]; dk and dv sum the
+   * contributions of the H / H_kv query heads of a group (in a fixed order: still bitwise repeatable).
+   * Only the single-evaluation tcgen05 kernels take H_kv != H. */
+  int32_t H_kv;
 } kb_sa_bwd_params;
 
 KB_API int kb_sa_bwd(const kb_sa_bwd_params* p, void* stream);

@@ -19,6 +19,7 @@ KB_F32, KB_F16, KB_BF16 = 0, 1, 2
 KB_FLAG_PRESCALE_QK, KB_FLAG_ALLOW_TF32, KB_FLAG_FORCE_GENERIC = 1, 2, 4
 KB_FLAG_BWD_SKIP_DQ, KB_FLAG_BWD_SKIP_DKDV, KB_FLAG_BWD_TWO_PASS, KB_FLAG_BWD_SKIP_DELTA = 8, 16, 32, 64
 KB_PATH_GENERIC, KB_PATH_SM100 = 0, 1
+KB_ERR_UNSUPPORTED = 2
 KB_NOALLOC_MAX_ROWS = 1 << 21
 
 _DTYPES = {torch.float32: KB_F32, torch.float16: KB_F16, torch.bfloat16: KB_BF16}
@@ -41,6 +42,7 @@ class SaFwdParams(C.Structure):
         ("B", C.c_int32), ("H", C.c_int32), ("T", C.c_int32), ("D", C.c_int32),
         ("dtype", C.c_int32), ("context_size", C.c_int32), ("back_contexts", C.c_int32),
         ("sm_scale", C.c_float), ("flags", C.c_uint32), ("status", C.c_void_p),
+        ("H_kv", C.c_int32),
     ]
 
 
@@ -54,6 +56,7 @@ class SaBwdParams(C.Structure):
         ("dtype", C.c_int32), ("context_size", C.c_int32), ("back_contexts", C.c_int32),
         ("sm_scale", C.c_float), ("flags", C.c_uint32), ("status", C.c_void_p),
         ("ds_ws", C.c_void_p), ("ds_ws_bytes", C.c_uint64),
+        ("H_kv", C.c_int32),
     ]
 
 

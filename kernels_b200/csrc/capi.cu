@@ -67,9 +67,18 @@ int select_bwd_path(const kb_sa_bwd_params& p) {
   return KB_PATH_GENERIC;
 }
 
+// heads of k / v: H unless the caller asked for shared key/value heads; -1 if the request is invalid
+template <typename P>
+int32_t kv_heads(const P* p) {
+  if (p->H_kv == 0 || p->H_kv == p->H) return p->H;
+  if (p->H_kv < 0 || p->H_kv > p->H || p->H % p->H_kv) return -1;
+  return p->H_kv;
+}
+
 int run_fwd(const kb_sa_fwd_params* p, void* stream, bool dense) {
   int rc = check_common(p);
   if (rc) return rc;
+  if (kv_heads(p) < 0) return KB_ERR_BAD_ARGUMENT;
   if (!dense && (p->context_size < 1 || p->back_contexts < 0)) return KB_ERR_BAD_ARGUMENT;
   if (empty(p->B, p->H, p->T)) return KB_OK;
   if (!p->q.data || !p->k.data || !p->v.data || !p->o) return KB_ERR_BAD_ARGUMENT;
@@ -84,6 +93,7 @@ int run_fwd(const kb_sa_fwd_params* p, void* stream, bool dense) {
     if (rc != KB_ERR_UNSUPPORTED) return rc;
   }
 #endif
+  if (kv_heads(p) != p->H) return KB_ERR_UNSUPPORTED;  // the generic kernels want one K/V head per query head
   return sa_fwd_generic(*p, c, back, s);
 }
 
@@ -99,7 +109,7 @@ int kb_fa_fwd(const kb_sa_fwd_params* p, void* stream) { return kb::run_fwd(p, s
 int kb_sa_bwd(const kb_sa_bwd_params* p, void* stream) {
   int rc = kb::check_common(p);
   if (rc) return rc;
-  if (p->context_size < 1 || p->back_contexts < 0) return KB_ERR_BAD_ARGUMENT;
+  if (p->context_size < 1 || p->back_contexts < 0 || kb::kv_heads(p) < 0) return KB_ERR_BAD_ARGUMENT;
   if (kb::empty(p->B, p->H, p->T)) return KB_OK;
   if (!p->q.data || !p->k.data || !p->v.data || !p->o.data || !p->d_o.data || !p->lse || !p->dq || !p->dk ||
       !p->dv || !p->delta_ws)
@@ -116,10 +126,12 @@ int kb_sa_bwd(const kb_sa_bwd_params* p, void* stream) {
       if (rc != KB_ERR_UNSUPPORTED) return rc;
     }
 #endif
+    if (kb::kv_heads(p) != p->H) return KB_ERR_UNSUPPORTED;  // shared K/V heads: single-evaluation kernels only
     const int rc = kb::sa_bwd_sm100(*p, c, back, s);
     if (rc != KB_ERR_UNSUPPORTED) return rc;
   }
 #endif
+  if (kb::kv_heads(p) != p->H) return KB_ERR_UNSUPPORTED;
   return kb::sa_bwd_generic(*p, c, back, s);
 }
 

@@ -89,7 +89,8 @@ struct FusedArgs {
   const int32_t* lens;
   int64_t lens_stride;
   int32_t B, H, T, c, back, W;
-  KbFastDiv fd_tiles, fd_H, fd_c;  // division by ceil(T / 128), H and c
+  int32_t Hk, group;  // key/value heads and query heads per key/value head (H = Hk * group)
+  KbFastDiv fd_tiles, fd_H, fd_Hk, fd_group, fd_c;  // division by ceil(T / 128), H, Hk, group and c
   float scale_log2, sm_scale;
   int32_t* status;
 };
@@ -130,15 +131,20 @@ constexpr int kErrSmemAlign = 71;
 // role walks the same sequence with its own cursor: `n` counts the live items so far, `g` the tiles
 // so far; barrier phases are derived from them.
 struct Item {
-  int b, h, kt, k0, len;
-  KbTileRange qr;  // query tiles [begin, end) of 128 rows that send gradient to this key tile
+  int b, hk, kt, k0, len;  // hk: key/value head
+  KbTileRange qr;          // query tiles [begin, end) of 128 rows that send gradient to this key tile
 };
+// The tiles of an item: for every query head of the key/value head's group (hq = 0 .. group - 1), the
+// query tiles of `qr` (tq = 0 ..); t is the running index over both.
 struct Cursor {
-  int item, n, g, t;
+  int item, n, g, t, tq, hq, group;
   Item it;
   bool valid;
-  __device__ __forceinline__ int tiles() const { return it.qr.end - it.qr.begin; }
+  __device__ __forceinline__ int q_tiles() const { return it.qr.end - it.qr.begin; }
+  __device__ __forceinline__ int tiles() const { return group * q_tiles(); }
   __device__ __forceinline__ bool last() const { return t == tiles() - 1; }
+  __device__ __forceinline__ int head() const { return it.hk * group + hq; }       // query head of the tile
+  __device__ __forceinline__ int q0() const { return (it.qr.begin + tq) * kBQ; }   // its first query row
 };
 
 // `prev` is the item decoded before (b = -1: none): consecutive items mostly share the batch index
@@ -147,8 +153,8 @@ __device__ __forceinline__ Item decode_item(const FusedArgs& a, int item, int n_
   Item it;
   const int bh = kb_fastdiv(item, a.fd_tiles);
   it.kt = item - bh * n_ktiles;
-  it.b = kb_fastdiv(bh, a.fd_H);
-  it.h = bh - it.b * a.H;
+  it.b = kb_fastdiv(bh, a.fd_Hk);
+  it.hk = bh - it.b * a.Hk;
   it.k0 = it.kt * kBK;
   it.len = !a.lens ? a.T : (it.b == prev.b ? prev.len : kb_clamp_len(a.lens[(int64_t)it.b * a.lens_stride], a.T));
   it.qr = kb_bwd_q_range_fd(it.k0, kBQ, kBK, it.len, a.c, a.back, a.fd_c);
@@ -168,19 +174,25 @@ __device__ __forceinline__ void seek_live(const FusedArgs& a, Cursor& c, int n_i
 __device__ __forceinline__ Cursor cursor_first(const FusedArgs& a, int n_items, int n_ktiles) {
   Cursor c;
   c.item = blockIdx.x;
-  c.n = c.g = c.t = 0;
+  c.n = c.g = c.t = c.tq = c.hq = 0;
+  c.group = a.group;
   c.it.b = -1;
   seek_live(a, c, n_items, n_ktiles);
   return c;
 }
 __device__ __forceinline__ void cursor_next(const FusedArgs& a, Cursor& c, int n_items, int n_ktiles) {
   ++c.g;
-  if (++c.t < c.tiles()) return;
+  ++c.t;
+  if (++c.tq < c.q_tiles()) return;
+  c.tq = 0;
+  if (++c.hq < c.group) return;
+  c.hq = 0;
   c.t = 0;
   ++c.n;
   c.item += gridDim.x;
   seek_live(a, c, n_items, n_ktiles);
 }
+// `h` is the QUERY head
 __device__ __forceinline__ uint8_t* ds_slot(const FusedArgs& a, int b, int h, int kt, int n_ktiles, int slot) {
   return a.ds_ws + ((((int64_t)b * a.H + h) * n_ktiles + kt) * a.W + slot) * (int64_t)kDsTileBytes;
 }
@@ -197,7 +209,7 @@ sa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int T = a.T;
   const int n_ktiles = kb_cdiv_i32(T, kBK);
-  const int n_items = a.B * a.H * n_ktiles;
+  const int n_items = a.B * a.Hk * n_ktiles;
 
   if (smem_u32(smem_raw) & 1023u) {
     // swizzled operand tiles need a 1024-byte aligned base: report instead of computing garbage
@@ -260,7 +272,7 @@ sa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
       bool ok = true;
       for (Cursor c = cursor_first(a, n_items, n_ktiles); ok && c.valid; cursor_next(a, c, n_items, n_ktiles)) {
         const int g = c.g, n = c.n;
-        const int q0 = (c.it.qr.begin + c.t) * kBQ;
+        const int q0 = c.q0(), hq = c.head();
         if (lane == 0) {
           KB_FTR(0, g, 0);
           // order of issue = order of need: S wants K and Q, dP (issued a tile later) wants V and dO
@@ -273,8 +285,8 @@ sa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
             if (nx.valid) {
 #pragma unroll
               for (int p = 0; p < kPanels; ++p) {
-                tma_prefetch_l2_4d(&tm_k, p * 64, nx.it.k0, nx.it.h, nx.it.b);
-                tma_prefetch_l2_4d(&tm_v, p * 64, nx.it.k0, nx.it.h, nx.it.b);
+                tma_prefetch_l2_4d(&tm_k, p * 64, nx.it.k0, nx.it.hk, nx.it.b);
+                tma_prefetch_l2_4d(&tm_v, p * 64, nx.it.k0, nx.it.hk, nx.it.b);
               }
             }
             const int ks = n & 1;
@@ -284,7 +296,7 @@ sa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
               mbar_expect_tx(&sm.k_full[ks], kTileBytes);
 #pragma unroll
               for (int p = 0; p < kPanels; ++p)
-                tma_load_4d(sm.k[ks] + p * kPanelBytes, &tm_k, &sm.k_full[ks], p * 64, c.it.k0, c.it.h, c.it.b);
+                tma_load_4d(sm.k[ks] + p * kPanelBytes, &tm_k, &sm.k_full[ks], p * 64, c.it.k0, c.it.hk, c.it.b);
             }
           }
           if (ok && g >= 2) ok = mbar_wait<kRelaxedNs>(&sm.q_empty[g & 1], ((g >> 1) - 1) & 1, ctx, kWQEmpty);
@@ -292,7 +304,7 @@ sa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
             mbar_expect_tx(&sm.q_full[g & 1], kTileBytes);
 #pragma unroll
             for (int p = 0; p < kPanels; ++p)
-              tma_load_4d(sm.q[g & 1] + p * kPanelBytes, &tm_q, &sm.q_full[g & 1], p * 64, q0, c.it.h, c.it.b);
+              tma_load_4d(sm.q[g & 1] + p * kPanelBytes, &tm_q, &sm.q_full[g & 1], p * 64, q0, hq, c.it.b);
           }
           KB_FTR(0, g, 1);
           if (ok && c.t == 0) {
@@ -301,7 +313,7 @@ sa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
               mbar_expect_tx(&sm.v_full, kTileBytes);
 #pragma unroll
               for (int p = 0; p < kPanels; ++p)
-                tma_load_4d(sm.v + p * kPanelBytes, &tm_v, &sm.v_full, p * 64, c.it.k0, c.it.h, c.it.b);
+                tma_load_4d(sm.v + p * kPanelBytes, &tm_v, &sm.v_full, p * 64, c.it.k0, c.it.hk, c.it.b);
             }
           }
           if (ok && g >= 1) ok = mbar_wait<kRelaxedNs>(&sm.do_empty, (g - 1) & 1, ctx, kWDoEmpty);
@@ -309,7 +321,7 @@ sa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
             mbar_expect_tx(&sm.do_full, kTileBytes);
 #pragma unroll
             for (int p = 0; p < kPanels; ++p)
-              tma_load_4d(sm.d_o + p * kPanelBytes, &tm_do, &sm.do_full, p * 64, q0, c.it.h, c.it.b);
+              tma_load_4d(sm.d_o + p * kPanelBytes, &tm_do, &sm.do_full, p * 64, q0, hq, c.it.b);
           }
           KB_FTR(0, g, 2);
         }
@@ -318,7 +330,7 @@ sa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
         if (ok && g >= 2) ok = mbar_wait<kRelaxedNs>(&sm.ds_ready[g & 1], ((g >> 1) - 1) & 1, ctx, kWStatsSlot);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
-        const int64_t bh = (int64_t)c.it.b * a.H + c.it.h;
+        const int64_t bh = (int64_t)c.it.b * a.H + hq;
 #pragma unroll
         for (int i = 0; i < kBQ / 32; ++i) {
           const int r = q0 + lane + 32 * i;
@@ -442,7 +454,7 @@ sa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
       // ------------------------------ dS tiles to the scratch buffer ------------------------------
       for (Cursor c = cursor_first(a, n_items, n_ktiles); c.valid; cursor_next(a, c, n_items, n_ktiles)) {
         if (!mbar_wait<kRelaxedNs>(&sm.ds_ready[c.g & 1], (c.g >> 1) & 1, ctx, kWSpill)) break;
-        bulk_store(ds_slot(a, c.it.b, c.it.h, c.it.kt, n_ktiles, c.t), sm.ds, kDsTileBytes);
+        bulk_store(ds_slot(a, c.it.b, c.head(), c.it.kt, n_ktiles, c.tq), sm.ds, kDsTileBytes);
         tma_store_commit();
         tma_store_wait_read();
         mbar_arrive(&sm.ds_free);  // the compute warps may form the next dS in the buffer
@@ -473,7 +485,7 @@ sa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
           hi = h64 < c.it.len ? (int)h64 : c.it.len;
         }
       }
-      const int y0 = (c.it.qr.begin + c.t) * kBQ + half * 64;  // first query column this thread handles
+      const int y0 = c.q0() + half * 64;  // first query column this thread handles
       const float* lse_c = sm.lse_s[g & 1] + half * 64;
       const float* delta_c = sm.delta_s[g & 1] + half * 64;
 
@@ -566,7 +578,7 @@ sa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
     it.b = -1;
     for (int item = blockIdx.x; ok && item < n_items; item += gridDim.x) {
       it = decode_item(a, item, n_ktiles, it);
-      const int64_t bh = (int64_t)it.b * a.H + it.h;
+      const int64_t bh = (int64_t)it.b * a.Hk + it.hk;  // dV and dK have one head per key/value head
       const int kr = it.k0 + row;
       if (it.qr.begin >= it.qr.end) {
         // the whole key tile lies in the padding: its gradients are zeros (rare; plain stores)
@@ -617,7 +629,7 @@ sa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
         if (etid == 0) {
 #pragma unroll
           for (int p = 0; p < kPanels; ++p)
-            tma_store_4d(which ? &tm_dk : &tm_dv, stage + p * kPanelBytes, p * 64, it.k0, it.h, it.b);
+            tma_store_4d(which ? &tm_dk : &tm_dv, stage + p * kPanelBytes, p * 64, it.k0, it.hk, it.b);
           tma_store_commit();
           tma_store_wait_read();
           if (which == 1) mbar_arrive(&sm.k_free[n & 1]);  // K(n + 2) may land in the buffer
@@ -798,7 +810,7 @@ sa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
           bulk_load(sm.ds[s], ds_slot(a, it.b, it.h, j, n_tiles_t, it.qt - qr.begin), kDsTileBytes, &sm.full[s]);
 #pragma unroll
           for (int p = 0; p < kPanels; ++p)
-            tma_load_4d(sm.k[s] + p * kPanelBytes, &tm_k, &sm.full[s], p * 64, j * kBK, it.h, it.b);
+            tma_load_4d(sm.k[s] + p * kPanelBytes, &tm_k, &sm.full[s], p * 64, j * kBK, kb_fastdiv(it.h, a.fd_group), it.b);
         }
       }
     }
@@ -898,10 +910,11 @@ sa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
 template <int D, bool BF16>
 int launch_fused(const kb_sa_bwd_params& p, int32_t c, int32_t back, cudaStream_t s) {
   CUtensorMap tm_k, tm_v, tm_q, tm_do, tm_dk, tm_dv, tm_dq;
-  if (!make_tile_map_4d(&tm_k, p.k, p.B, p.H, p.T, D, kBK) || !make_tile_map_4d(&tm_v, p.v, p.B, p.H, p.T, D, kBK) ||
+  const int32_t Hk = p.H_kv > 0 ? p.H_kv : p.H;
+  if (!make_tile_map_4d(&tm_k, p.k, p.B, Hk, p.T, D, kBK) || !make_tile_map_4d(&tm_v, p.v, p.B, Hk, p.T, D, kBK) ||
       !make_tile_map_4d(&tm_q, p.q, p.B, p.H, p.T, D, kBQ) || !make_tile_map_4d(&tm_do, p.d_o, p.B, p.H, p.T, D, kBQ) ||
-      !make_tile_map_4d_contiguous(&tm_dk, p.dk, p.B, p.H, p.T, D, kBK) ||
-      !make_tile_map_4d_contiguous(&tm_dv, p.dv, p.B, p.H, p.T, D, kBK) ||
+      !make_tile_map_4d_contiguous(&tm_dk, p.dk, p.B, Hk, p.T, D, kBK) ||
+      !make_tile_map_4d_contiguous(&tm_dv, p.dv, p.B, Hk, p.T, D, kBK) ||
       !make_tile_map_4d_contiguous(&tm_dq, p.dq, p.B, p.H, p.T, D, kBQ))
     return KB_ERR_UNSUPPORTED;
   const int n_tiles = kb_cdiv_i32(p.T, kBQ);
@@ -910,7 +923,9 @@ int launch_fused(const kb_sa_bwd_params& p, int32_t c, int32_t back, cudaStream_
   int dev = 0, n_sm = 0;
   KB_CUDA_TRY(cudaGetDevice(&dev));
   KB_CUDA_TRY(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev));
-  const unsigned grid = (unsigned)(n_items < n_sm ? n_items : n_sm);  // persistent: one CTA per SM
+  const unsigned grid = (unsigned)(n_items < n_sm ? n_items : n_sm);  // persistent: one CTA per SM (dQ kernel)
+  const int64_t n_items_main = (int64_t)p.B * Hk * n_tiles;
+  const unsigned grid_main = (unsigned)(n_items_main < n_sm ? n_items_main : n_sm);
 
   auto main_kern = sa_bwd_fused_kernel<D, BF16>;
   auto dq_kern = sa_bwd_dq_kernel<D, BF16>;
@@ -953,13 +968,17 @@ int launch_fused(const kb_sa_bwd_params& p, int32_t c, int32_t back, cudaStream_
   fa.back = back;
   fa.W = fused_slots(p.T, c, back);
   fa.fd_tiles = kb_fastdiv_make(n_tiles);
+  fa.Hk = Hk;
+  fa.group = p.H / Hk;
   fa.fd_H = kb_fastdiv_make(p.H);
+  fa.fd_Hk = kb_fastdiv_make(Hk);
+  fa.fd_group = kb_fastdiv_make(p.H / Hk);
   fa.fd_c = kb_fastdiv_make(c);
   fa.scale_log2 = p.sm_scale * kLog2e;
   fa.sm_scale = p.sm_scale;
   fa.status = p.status;
   if (!(p.flags & KB_FLAG_BWD_SKIP_DKDV)) {
-    main_kern<<<grid, kThreads, sizeof(FusedSmem<D>), s>>>(tm_k, tm_v, tm_q, tm_do, tm_dk, tm_dv, fa);
+    main_kern<<<grid_main, kThreads, sizeof(FusedSmem<D>), s>>>(tm_k, tm_v, tm_q, tm_do, tm_dk, tm_dv, fa);
     KB_LAUNCH_CHECK("sa_bwd_fused_kernel");
   }
   if (!(p.flags & KB_FLAG_BWD_SKIP_DQ)) {

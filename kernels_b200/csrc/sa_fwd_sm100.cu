@@ -60,7 +60,7 @@ struct FwdArgs {
   const int32_t* lens;
   int64_t lens_stride;
   int32_t B, H, T, c, back;
-  KbFastDiv fd_qblocks, fd_H, fd_c;  // division by ceil(T / 256), H and c
+  KbFastDiv fd_qblocks, fd_H, fd_c, fd_group;  // division by ceil(T / 256), H, c and H / H_kv (query heads per K/V head)
   float scale_log2;
   int32_t* status;
 };
@@ -230,17 +230,18 @@ sa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
           for (int p = 0; p < kPanels; ++p)
             tma_load_4d(sm.q[x] + p * kPanelBytes, &tm_q, &sm.q_full, p * 64, it.q0 + x * kBM, it.h, it.b);
         }
+        const int h_kv = kb_fastdiv(it.h, a.fd_group);  // the K/V head this query head reads
         for (int t = it.u_begin; t < it.u_end; ++t, ++kc, ++vc) {
           const int sk = kc % kStagesK, sv = vc % kStagesV;
           const int k0 = t * kBN;
           if (kc >= kStagesK && !mbar_wait(&sm.k_empty[sk], ((kc / kStagesK) - 1) & 1, ctx, kWaitKEmpty)) { ok = false; break; }
           mbar_expect_tx(&sm.k_full[sk], kTileBytes);
 #pragma unroll
-          for (int p = 0; p < kPanels; ++p) tma_load_4d(sm.k[sk] + p * kPanelBytes, &tm_k, &sm.k_full[sk], p * 64, k0, it.h, it.b);
+          for (int p = 0; p < kPanels; ++p) tma_load_4d(sm.k[sk] + p * kPanelBytes, &tm_k, &sm.k_full[sk], p * 64, k0, h_kv, it.b);
           if (vc >= kStagesV && !mbar_wait(&sm.v_empty[sv], ((vc / kStagesV) - 1) & 1, ctx, kWaitVEmpty)) { ok = false; break; }
           mbar_expect_tx(&sm.v_full[sv], kTileBytes);
 #pragma unroll
-          for (int p = 0; p < kPanels; ++p) tma_load_4d(sm.v[sv] + p * kPanelBytes, &tm_v, &sm.v_full[sv], p * 64, k0, it.h, it.b);
+          for (int p = 0; p < kPanels; ++p) tma_load_4d(sm.v[sv] + p * kPanelBytes, &tm_v, &sm.v_full[sv], p * 64, k0, h_kv, it.b);
         }
         ++na;
       }
@@ -414,8 +415,9 @@ sa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
 template <int D, bool BF16>
 int launch(const kb_sa_fwd_params& p, int32_t c, int32_t back, cudaStream_t s) {
   CUtensorMap tm_q, tm_k, tm_v;
-  if (!make_tile_map_4d(&tm_q, p.q, p.B, p.H, p.T, D, kBM) || !make_tile_map_4d(&tm_k, p.k, p.B, p.H, p.T, D, kBN) ||
-      !make_tile_map_4d(&tm_v, p.v, p.B, p.H, p.T, D, kBN))
+  const int32_t H_kv = p.H_kv > 0 ? p.H_kv : p.H;
+  if (!make_tile_map_4d(&tm_q, p.q, p.B, p.H, p.T, D, kBM) || !make_tile_map_4d(&tm_k, p.k, p.B, H_kv, p.T, D, kBN) ||
+      !make_tile_map_4d(&tm_v, p.v, p.B, H_kv, p.T, D, kBN))
     return KB_ERR_UNSUPPORTED;
   auto kern = sa_fwd_sm100_kernel<D, BF16>;
   constexpr size_t smem = sizeof(FwdSmem<D>);
@@ -434,6 +436,7 @@ int launch(const kb_sa_fwd_params& p, int32_t c, int32_t back, cudaStream_t s) {
   a.fd_qblocks = kb_fastdiv_make(kb_cdiv_i32(p.T, kBM * kQTiles));
   a.fd_H = kb_fastdiv_make(p.H);
   a.fd_c = kb_fastdiv_make(c);
+  a.fd_group = kb_fastdiv_make(p.H / H_kv);
   a.scale_log2 = p.sm_scale * kLog2e;
   a.status = p.status;
   const int64_t n_items = (int64_t)p.B * p.H * kb_cdiv_i32(p.T, kBM * kQTiles);

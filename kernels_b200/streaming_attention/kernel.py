@@ -55,7 +55,10 @@ def _check_inputs(q, k, v, lens, context_size, back_contexts, sm_scale):
     assert D in _SUPPORTED_HEAD_DIMS
     assert D == k.shape[-1] and D == v.shape[-1]
     assert T == k.shape[-2] and T == v.shape[-2]
-    assert q.shape[:2] == k.shape[:2] == v.shape[:2]
+    # the reference wants q.shape[:2] == k.shape[:2] (kernel.py:1291); here k and v may also carry fewer
+    # heads that divide the query heads (shared key/value heads): query head h reads head h // (H // H_kv)
+    assert k.shape == v.shape and q.shape[0] == k.shape[0]
+    assert k.shape[1] >= 1 and q.shape[1] % k.shape[1] == 0
     assert q.dtype == k.dtype == v.dtype
     assert sm_scale is not None
     assert lens is None or (lens.dtype == torch.int32 and batch == len(lens) and lens.ndim == 1)
@@ -111,8 +114,15 @@ def attention_forward_adapter(
     p.sm_scale = float(sm_scale)
     p.flags = _flags(prescale_qk, precision)
     p.status = _lib.status_words().data_ptr()
+    p.H_kv = k.shape[1]
     with torch.cuda.device(q.device):
-        rc = lib.kb_sa_fwd(ctypes.byref(p), torch.cuda.current_stream(q.device).cuda_stream)
+        stream = torch.cuda.current_stream(q.device).cuda_stream
+        rc = lib.kb_sa_fwd(ctypes.byref(p), stream)
+        if rc == _lib.KB_ERR_UNSUPPORTED and k.shape[1] != H:
+            # no kernel with shared key/value heads for this dtype / head_dim / layout: repeat the heads
+            k_rep, v_rep = (t.repeat_interleave(H // t.shape[1], dim=1) for t in (k, v))
+            p.k, p.v, p.H_kv = _lib.tensor4(k_rep), _lib.tensor4(v_rep), H
+            rc = lib.kb_sa_fwd(ctypes.byref(p), stream)
     _lib.check(rc, "kb_sa_fwd")
     del lens_keep
 
@@ -200,8 +210,22 @@ def attention_backward_adapter(
     p.sm_scale = float(sm_scale)
     p.flags = _flags(prescale_qk, precision)
     p.status = _lib.status_words().data_ptr()
+    p.H_kv = k.shape[1]
     with torch.cuda.device(q.device):
-        rc = lib.kb_sa_bwd(ctypes.byref(p), torch.cuda.current_stream(q.device).cuda_stream)
+        stream = torch.cuda.current_stream(q.device).cuda_stream
+        rc = lib.kb_sa_bwd(ctypes.byref(p), stream)
+        if rc == _lib.KB_ERR_UNSUPPORTED and k.shape[1] != H:
+            # no kernel with shared key/value heads for this call: repeat the heads, then add up the
+            # gradients of a group's copies
+            group = H // k.shape[1]
+            k_rep, v_rep = (t.repeat_interleave(group, dim=1) for t in (k, v))
+            dk_rep, dv_rep = torch.empty_like(k_rep), torch.empty_like(v_rep)
+            p.k, p.v, p.H_kv = _lib.tensor4(k_rep), _lib.tensor4(v_rep), H
+            p.dk, p.dv = dk_rep.data_ptr(), dv_rep.data_ptr()
+            rc = lib.kb_sa_bwd(ctypes.byref(p), stream)
+            if rc == 0:
+                DK.copy_(dk_rep.view(B, k.shape[1], group, T, D).float().sum(dim=2))
+                DV.copy_(dv_rep.view(B, k.shape[1], group, T, D).float().sum(dim=2))
     _lib.check(rc, "kb_sa_bwd")
     del lens_keep
     return DQ, DK, DV
@@ -302,7 +326,9 @@ def streaming_attention(
 
     Args:
         q, k, v: ``(batch, heads, time, head_dim)``; fp32, fp16 or bf16; any strides;
-            ``head_dim`` in {16, 32, 64, 128, 256}.
+            ``head_dim`` in {16, 32, 64, 128, 256}.  ``k`` and ``v`` may have fewer heads than ``q``
+            (a divisor of its head count): consecutive groups of query heads then share a key/value
+            head (an extension; the reference requires equal head counts).
         lens: optional int32 ``(batch,)`` sequence lengths; positions ``>= lens[b]`` neither
             attend nor are attended to, and their output rows are 0.
         context_size: chunk length in tokens (>= 1).
