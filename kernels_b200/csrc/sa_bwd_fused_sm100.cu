@@ -362,11 +362,11 @@ sa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
         if (!mbar_wait(&sm.q_full[c.g & 1], (c.g >> 1) & 1, ctx, kWQFull)) return false;
         KB_ACC(9);  // waits for K, Q (counted apart from the issue of S)
         tc_fence_after();
-        const uint32_t k_addr = smem_u32(sm.k[c.n & 1]), q_addr = smem_u32(sm.q[c.g & 1]);
+        uint32_t k_lo = desc_lo_kmajor(smem_u32(sm.k[c.n & 1])), q_lo = desc_lo_kmajor(smem_u32(sm.q[c.g & 1]));
 #pragma unroll 1
-        for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = (kk / 4) * kPanelBytes + (kk % 4) * 32;
-          mma_ss(tmem + kColS, desc_kmajor(k_addr + off), desc_kmajor(q_addr + off), idesc_z, kk > 0);
+        for (int p = 0; p < D / 64; ++p, k_lo += kPanelBytes >> 4, q_lo += kPanelBytes >> 4) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) mma_ss_lo(tmem + kColS, k_lo + 2 * i, q_lo + 2 * i, idesc_z, p > 0 || i > 0);
         }
         mma_commit(&sm.s_ready);
         return true;
@@ -377,10 +377,11 @@ sa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
         if (!mbar_wait(&sm.do_full, c.g & 1, ctx, kWDoFull)) return false;
         KB_ACC(10);  // waits for V, dO (counted apart from the issue of dP)
         tc_fence_after();
+        uint32_t v_lo = desc_lo_kmajor(v_addr), do_lo = desc_lo_kmajor(do_addr);
 #pragma unroll 1
-        for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = (kk / 4) * kPanelBytes + (kk % 4) * 32;
-          mma_ss(tmem + kColDP, desc_kmajor(v_addr + off), desc_kmajor(do_addr + off), idesc_z, kk > 0);
+        for (int p = 0; p < D / 64; ++p, v_lo += kPanelBytes >> 4, do_lo += kPanelBytes >> 4) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) mma_ss_lo(tmem + kColDP, v_lo + 2 * i, do_lo + 2 * i, idesc_z, p > 0 || i > 0);
         }
         mma_commit(&sm.dp_ready);
         if (c.last()) mma_commit(&sm.v_empty);  // V of this item has no reader left
@@ -388,13 +389,13 @@ sa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
       };
       // acc += A(tmem, 16-bit at `a_col`) * B(smem tile at b_addr, MN-major)
       auto issue_acc = [&](uint32_t acc_col, uint32_t a_col, uint32_t b_addr, bool first_tile) {
+        // 16 queries = 8 packed columns; queries [64 w, 64 w + 64) sit at columns 64 w ..
+        uint32_t a = tmem + a_col, b_lo = desc_lo_mnmajor(b_addr, kPanelBytes);
 #pragma unroll 1
-        for (int kk = 0; kk < kBQ / 16; ++kk) {
-          // 16 queries = 8 packed columns; queries [64 w, 64 w + 64) sit at columns 64 w ..
-          const uint32_t ko = (kk / 4) * 64 + (kk % 4) * 8;
-
-          mma_ts(tmem + acc_col, tmem + a_col + ko, desc_mnmajor(b_addr + kk * 2048, kPanelBytes), idesc_acc,
-                 !first_tile || kk > 0);
+        for (int p = 0; p < kBQ / 64; ++p, a += 64, b_lo += 4 * (2048 >> 4)) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            mma_ts_lo(tmem + acc_col, a + 8 * i, b_lo + i * (2048 >> 4), idesc_acc, !first_tile || p > 0 || i > 0);
         }
       };
 
@@ -503,17 +504,30 @@ sa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
         tmem_ld32(t_s, reinterpret_cast<uint32_t(&)[32]>(s[0]));
         tmem_ld32(t_s + 32, reinterpret_cast<uint32_t(&)[32]>(s[32]));
         tmem_wait_ld();
+        // 32 columns at a time, with warp-wide votes when the block is not live throughout: a group that
+        // is masked for every row of the warp needs no exponentials, one that is live for every row no
+        // selects (chunk boundaries that are multiples of 32 never leave a mixed group)
 #pragma unroll
-        for (int i = 0; i < 64; i += 4) {
-          const float4 lv = *reinterpret_cast<const float4*>(lse_c + i);
-          p[i + 0] = ex2_approx(fmaf(__uint_as_float(s[i + 0]), scale, -lv.x));
-          p[i + 1] = ex2_approx(fmaf(__uint_as_float(s[i + 1]), scale, -lv.y));
-          p[i + 2] = ex2_approx(fmaf(__uint_as_float(s[i + 2]), scale, -lv.z));
-          p[i + 3] = ex2_approx(fmaf(__uint_as_float(s[i + 3]), scale, -lv.w));
-        }
-        if (!warp_full) {
+        for (int cc = 0; cc < 2; ++cc) {
+          const int c0 = y0 + cc * 32;
+          const bool all_dead = !warp_full && __all_sync(0xffffffffu, c0 + 32 <= lo || c0 >= hi);
+          if (all_dead) {
 #pragma unroll
-          for (int i = 0; i < 64; ++i) p[i] = (y0 + i >= lo && y0 + i < hi) ? p[i] : 0.f;
+            for (int i = 0; i < 32; ++i) p[cc * 32 + i] = 0.f;
+            continue;
+          }
+#pragma unroll
+          for (int i = cc * 32; i < cc * 32 + 32; i += 4) {
+            const float4 lv = *reinterpret_cast<const float4*>(lse_c + i);
+            p[i + 0] = ex2_approx(fmaf(__uint_as_float(s[i + 0]), scale, -lv.x));
+            p[i + 1] = ex2_approx(fmaf(__uint_as_float(s[i + 1]), scale, -lv.y));
+            p[i + 2] = ex2_approx(fmaf(__uint_as_float(s[i + 2]), scale, -lv.z));
+            p[i + 3] = ex2_approx(fmaf(__uint_as_float(s[i + 3]), scale, -lv.w));
+          }
+          if (!warp_full && !__all_sync(0xffffffffu, lo <= c0 && c0 + 32 <= hi)) {
+#pragma unroll
+            for (int i = cc * 32; i < cc * 32 + 32; ++i) p[i] = (y0 + i >= lo && y0 + i < hi) ? p[i] : 0.f;
+          }
         }
       }
 #pragma unroll
@@ -830,11 +844,13 @@ sa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
           const int s = u % kDqStages;
           if (!mbar_wait(&sm.full[s], (u / kDqStages) & 1, ctx, kWDqFull)) { ok = false; break; }
           tc_fence_after();
-          const uint32_t ds_addr = smem_u32(sm.ds[s]), k_addr = smem_u32(sm.k[s]);
+          uint32_t ds_lo = desc_lo_mnmajor(smem_u32(sm.ds[s]), kPanelBytes), k_lo = desc_lo_mnmajor(smem_u32(sm.k[s]), kPanelBytes);
+#pragma unroll 1
+          for (int h = 0; h < kBK / 64; ++h, ds_lo += 4 * (2048 >> 4), k_lo += 4 * (2048 >> 4)) {
 #pragma unroll
-          for (int kk = 0; kk < kBK / 16; ++kk)
-            mma_ss(acc, desc_mnmajor(ds_addr + kk * 2048, kPanelBytes), desc_mnmajor(k_addr + kk * 2048, kPanelBytes), idesc,
-                   j > it.kr.begin || kk > 0);
+            for (int i = 0; i < 4; ++i)
+              mma_ss_lo(acc, ds_lo + i * (2048 >> 4), k_lo + i * (2048 >> 4), idesc, j > it.kr.begin || h > 0 || i > 0);
+          }
           mma_commit(&sm.empty[s]);
         }
         if (ok) mma_commit(&sm.acc_done[m & 1]);

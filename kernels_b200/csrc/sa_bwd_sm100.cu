@@ -251,10 +251,11 @@ sa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_a1, const __grid_cons
         tc_fence_after();
         const uint32_t b_addr = smem_u32(sm.b1[s1]);
         const uint32_t d_col = tmem + (sbuf ? kColS1 : kColS);
+        uint32_t a_lo = desc_lo_kmajor(a1_addr), b_lo = desc_lo_kmajor(b_addr);
+#pragma unroll 1
+        for (int h = 0; h < D / 64; ++h, a_lo += kPanelBytes >> 4, b_lo += kPanelBytes >> 4) {
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = (kk / 4) * kPanelBytes + (kk % 4) * 32;
-          mma_ss(d_col, desc_kmajor(a1_addr + off), desc_kmajor(b_addr + off), idesc_z, kk > 0);
+          for (int i = 0; i < 4; ++i) mma_ss_lo(d_col, a_lo + 2 * i, b_lo + 2 * i, idesc_z, h > 0 || i > 0);
         }
         mma_commit(&sm.s_ready[sbuf]);
         KB_TR(1, t, 2);
@@ -267,10 +268,11 @@ sa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_a1, const __grid_cons
         KB_TR(1, t, 3);
         tc_fence_after();
         const uint32_t b_addr = smem_u32(sm.b2[s2]);
+        uint32_t a_lo = desc_lo_kmajor(a2_addr), b_lo = desc_lo_kmajor(b_addr);
+#pragma unroll 1
+        for (int h = 0; h < D / 64; ++h, a_lo += kPanelBytes >> 4, b_lo += kPanelBytes >> 4) {
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = (kk / 4) * kPanelBytes + (kk % 4) * 32;
-          mma_ss(tmem + kColDP, desc_kmajor(a2_addr + off), desc_kmajor(b_addr + off), idesc_z, kk > 0);
+          for (int i = 0; i < 4; ++i) mma_ss_lo(tmem + kColDP, a_lo + 2 * i, b_lo + 2 * i, idesc_z, h > 0 || i > 0);
         }
         if (kDQ) mma_commit(&sm.b2_empty[s2]);  // V_t has no other reader in the dQ pass
         mma_commit(&sm.dp_ready);
@@ -279,12 +281,13 @@ sa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_a1, const __grid_cons
       };
       // acc += A(tmem, 16-bit at `a_col`) * B(smem tile at b_addr, MN-major)
       auto issue_acc = [&](uint32_t acc_col, uint32_t a_col, uint32_t b_addr, bool first_tile) {
+        // 16 reduction rows = 8 packed columns; rows [64 g, 64 g + 64) sit at columns 64 g ..
+        uint32_t a = tmem + a_col, b_lo = desc_lo_mnmajor(b_addr, kPanelBytes);
+#pragma unroll 1
+        for (int h = 0; h < kBY / 64; ++h, a += 64, b_lo += 4 * (2048 >> 4)) {
 #pragma unroll
-        for (int kk = 0; kk < kBY / 16; ++kk) {
-          // 16 reduction rows = 8 packed columns; rows [64 g, 64 g + 64) sit at columns 64 g ..
-          const uint32_t ko = (kk / 4) * 64 + (kk % 4) * 8;
-          mma_ts(tmem + acc_col, tmem + a_col + ko, desc_mnmajor(b_addr + kk * 2048, kPanelBytes), idesc_acc,
-                 !first_tile || kk > 0);
+          for (int i = 0; i < 4; ++i)
+            mma_ts_lo(tmem + acc_col, a + 8 * i, b_lo + i * (2048 >> 4), idesc_acc, !first_tile || h > 0 || i > 0);
         }
       };
 

@@ -89,11 +89,23 @@ __device__ __forceinline__ float softmax_block(uint32_t t_s, float scale, int k0
 #pragma unroll
   for (int cc = 0; cc < kBN / 32; ++cc) tmem_ld32(t_s + cc * 32, reinterpret_cast<uint32_t(&)[32]>(s[cc * 32]));
   tmem_wait_ld();
+  // Masking works on 32-column groups with warp-wide votes: a group that is live for every row of the
+  // warp needs no select, one that is masked for every row needs no exponentials either (chunk
+  // boundaries that are multiples of 32 never leave a mixed group).
+  bool dead[kBN / 32] = {};
   if (kMasked) {
 #pragma unroll
-    for (int i = 0; i < kBN; ++i) {
-      const int col = k0 + i;
-      s[i] = (col >= lo && col < hi) ? s[i] : 0xff800000u;  // -inf
+    for (int cc = 0; cc < kBN / 32; ++cc) {
+      const int c0 = k0 + cc * 32;
+      const bool all_live = __all_sync(0xffffffffu, lo <= c0 && c0 + 32 <= hi);
+      dead[cc] = __all_sync(0xffffffffu, c0 + 32 <= lo || c0 >= hi);
+      if (!all_live) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const int col = c0 + i;
+          s[cc * 32 + i] = (col >= lo && col < hi) ? s[cc * 32 + i] : 0xff800000u;  // -inf
+        }
+      }
     }
   }
   float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
@@ -116,6 +128,12 @@ __device__ __forceinline__ float softmax_block(uint32_t t_s, float scale, int k0
 #pragma unroll
   for (int cc = 0; cc < kBN / 32; ++cc) {
     uint32_t pk[16];
+    if (kMasked && dead[cc]) {
+#pragma unroll
+      for (int i = 0; i < 16; ++i) pk[i] = 0u;
+      tmem_st16(t_s + cc * 16, pk);
+      continue;
+    }
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
       const float p0 = ex2_approx(fmaf(__uint_as_float(s[cc * 32 + 2 * i]), scale, -m_safe));
@@ -275,11 +293,14 @@ sa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
               // the first P V of an item overwrites O: the softmax warps must have read the old one
               if (lx == 0 && items_x[x] > 0 && !mbar_wait(&sm.o_free[x], (items_x[x] - 1) & 1, ctx, kWaitOFree)) { ok = false; break; }
               tc_fence_after();
-              const uint32_t v_addr = smem_u32(sm.v[sv]);
+              // short issue loops (four instructions per trip, descriptor low words stepped by adds): the
+              // scalar work between two MMAs is what the tensor pipe waits for
+              uint32_t p_col = tmem + kColS + x * 128, v_lo = desc_lo_mnmajor(smem_u32(sm.v[sv]), kPanelBytes);
+#pragma unroll 1
+              for (int h = 0; h < kBN / 64; ++h, p_col += 32, v_lo += 4 * (2048 >> 4)) {
 #pragma unroll
-              for (int kk = 0; kk < kBN / 16; ++kk) {
-                mma_ts(tmem + kColO + x * 128, tmem + kColS + x * 128 + kk * 8, desc_mnmajor(v_addr + kk * 2048, kPanelBytes),
-                       idesc_pv, lx > 0 || kk > 0);
+                for (int i = 0; i < 4; ++i)
+                  mma_ts_lo(tmem + kColO + x * 128, p_col + 8 * i, v_lo + i * (2048 >> 4), idesc_pv, lx > 0 || h > 0 || i > 0);
               }
               // V_u is free once the last q tile that uses it has consumed it
               const bool last_user = (x == kQTiles - 1) || !(u >= it.kr[1].begin && u < it.kr[1].end);
@@ -290,11 +311,11 @@ sa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
               const int ki = kbase + i, sk = ki % kStagesK;
               if (!mbar_wait(&sm.k_full[sk], (ki / kStagesK) & 1, ctx, kWaitKFull)) { ok = false; break; }
               tc_fence_after();
-              const uint32_t q_addr = smem_u32(sm.q[x]), k_addr = smem_u32(sm.k[sk]);
+              uint32_t q_lo = desc_lo_kmajor(smem_u32(sm.q[x])), k_lo = desc_lo_kmajor(smem_u32(sm.k[sk]));
+#pragma unroll 1
+              for (int h = 0; h < D / 64; ++h, q_lo += kPanelBytes >> 4, k_lo += kPanelBytes >> 4) {
 #pragma unroll
-              for (int kk = 0; kk < D / 16; ++kk) {
-                const uint32_t off = (kk / 4) * kPanelBytes + (kk % 4) * 32;
-                mma_ss(tmem + kColS + x * 128, desc_kmajor(q_addr + off), desc_kmajor(k_addr + off), idesc_qk, kk > 0);
+                for (int i = 0; i < 4; ++i) mma_ss_lo(tmem + kColS + x * 128, q_lo + 2 * i, k_lo + 2 * i, idesc_qk, h > 0 || i > 0);
               }
               const bool last_user = (x == kQTiles - 1) || !(t >= it.kr[1].begin && t < it.kr[1].end);
               if (last_user) mma_commit(&sm.k_empty[sk]);

@@ -22,6 +22,18 @@ def _built_library():
     return _lib.load()
 
 
+@pytest.fixture(scope="module", autouse=True)
+def _fresh_dynamo_cache():
+    """The public entry point is a ``torch.compile(fullgraph=True)`` function, as the reference's is
+    (src/streaming_attention/kernel.py:1566); a long run over many distinct shapes would meet dynamo's
+    recompile limit, so every test module starts from an empty cache, whatever order the modules run in
+    (the reference's tests reset it per test, tests/test_streaming_attention.py:50)."""
+    import torch
+
+    torch._dynamo.reset()
+    yield
+
+
 @pytest.fixture(scope="session")
 def golden():
     import numpy as np
