@@ -356,13 +356,13 @@ sa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
       // The eight instructions of a matmul are issued from rolled loops on purpose: the MMA thread shares
       // its instruction cache with compute warps that run long unrolled loops, and a short issue path
       // measured 4 % faster than the unrolled one.
-      // S(c) = K Q^T
-      auto issue_s = [&](const Cursor& c) -> bool {
-        if (c.t == 0 && !mbar_wait(&sm.k_full[c.n & 1], (c.n >> 1) & 1, ctx, kWKFull)) return false;
-        if (!mbar_wait(&sm.q_full[c.g & 1], (c.g >> 1) & 1, ctx, kWQFull)) return false;
+      // S of tile g (item n) = K Q^T;  `new_item`: the tile opens an item, whose K has to have arrived
+      auto issue_s = [&](int n, int g, bool new_item) -> bool {
+        if (new_item && !mbar_wait(&sm.k_full[n & 1], (n >> 1) & 1, ctx, kWKFull)) return false;
+        if (!mbar_wait(&sm.q_full[g & 1], (g >> 1) & 1, ctx, kWQFull)) return false;
         KB_ACC(9);  // waits for K, Q (counted apart from the issue of S)
         tc_fence_after();
-        uint32_t k_lo = desc_lo_kmajor(smem_u32(sm.k[c.n & 1])), q_lo = desc_lo_kmajor(smem_u32(sm.q[c.g & 1]));
+        uint32_t k_lo = desc_lo_kmajor(smem_u32(sm.k[n & 1])), q_lo = desc_lo_kmajor(smem_u32(sm.q[g & 1]));
 #pragma unroll 1
         for (int p = 0; p < D / 64; ++p, k_lo += kPanelBytes >> 4, q_lo += kPanelBytes >> 4) {
 #pragma unroll
@@ -371,10 +371,10 @@ sa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
         mma_commit(&sm.s_ready);
         return true;
       };
-      // dP(c) = V dO^T
-      auto issue_dp = [&](const Cursor& c) -> bool {
-        if (c.t == 0 && !mbar_wait(&sm.v_full, c.n & 1, ctx, kWVFull)) return false;
-        if (!mbar_wait(&sm.do_full, c.g & 1, ctx, kWDoFull)) return false;
+      // dP of tile g (item n) = V dO^T;  `last`: the tile closes its item
+      auto issue_dp = [&](int n, int g, bool new_item, bool last) -> bool {
+        if (new_item && !mbar_wait(&sm.v_full, n & 1, ctx, kWVFull)) return false;
+        if (!mbar_wait(&sm.do_full, g & 1, ctx, kWDoFull)) return false;
         KB_ACC(10);  // waits for V, dO (counted apart from the issue of dP)
         tc_fence_after();
         uint32_t v_lo = desc_lo_kmajor(v_addr), do_lo = desc_lo_kmajor(do_addr);
@@ -384,7 +384,7 @@ sa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
           for (int i = 0; i < 4; ++i) mma_ss_lo(tmem + kColDP, v_lo + 2 * i, do_lo + 2 * i, idesc_z, p > 0 || i > 0);
         }
         mma_commit(&sm.dp_ready);
-        if (c.last()) mma_commit(&sm.v_empty);  // V of this item has no reader left
+        if (last) mma_commit(&sm.v_empty);  // V of this item has no reader left
         return true;
       };
       // acc += A(tmem, 16-bit at `a_col`) * B(smem tile at b_addr, MN-major)
@@ -398,54 +398,70 @@ sa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
             mma_ts_lo(tmem + acc_col, a + 8 * i, b_lo + i * (2048 >> 4), idesc_acc, !first_tile || p > 0 || i > 0);
         }
       };
+      // This thread keeps no cursor: all it needs of the schedule is how many tiles each live item has.
+      // Tiles of the first live item at or after `item` (stride gridDim.x), 0 if there is none.
+      auto next_live = [&](int& item) -> int {
+        Item prev;
+        prev.b = -1;
+        for (; item < n_items; item += gridDim.x) {
+          const Item it = decode_item(a, item, n_ktiles, prev);
+          if (it.qr.begin < it.qr.end) return (it.qr.end - it.qr.begin) * a.group;
+        }
+        return 0;
+      };
 
-      Cursor cur = cursor_first(a, n_items, n_ktiles);
-      bool ok = cur.valid && issue_s(cur) && issue_dp(cur);
-      Cursor nxt = cur;
-      if (ok) cursor_next(a, nxt, n_items, n_ktiles);
+      int item = blockIdx.x;
+      int cnt = next_live(item);  // tiles of the current item
+      int n = 0, g = 0;           // live items, tiles so far
+      bool ok = cnt > 0 && issue_s(0, 0, true) && issue_dp(0, 0, true, cnt == 1);
       KB_ACC(11);
       while (ok) {
-        const int g = cur.g;
-
-        const bool first = cur.t == 0;
-        KB_FTR(1, g, 0);
-        // dV(g) += P(g) dO(g)
-        KB_ACC(0);  // cursor
-        if (!mbar_wait(&sm.p_ready, g & 1, ctx, kWPReady)) break;
-        KB_ACC(1);  // wait p_ready
-        // the first MMAs of an item overwrite dV / dK: the epilogue warps must have read the old ones
-        if (first && cur.n > 0 && !mbar_wait(&sm.dv_free, (cur.n - 1) & 1, ctx, kWAccFree)) break;
-        KB_FTR(1, g, 1);
-        KB_ACC(2);  // wait dv_free
-        tc_fence_after();
-        issue_acc(kColDV, kColS, do_addr, first);
-        mma_commit(&sm.do_empty);
-        if (cur.last()) mma_commit(&sm.dv_done);  // the epilogue warps start on dV while dK(last) still runs
-        KB_FTR(1, g, 2);
-        KB_ACC(3);  // issue dV
-        // S(g+1)
-        if (nxt.valid && !issue_s(nxt)) break;
-        KB_FTR(1, g, 3);
-        KB_ACC(4);  // S(g+1) incl. waits for K, Q
-        // dK(g) += dS(g) Q(g)
-        if (!mbar_wait(&sm.ds_ready[g & 1], (g >> 1) & 1, ctx, kWDsReady)) break;
-        KB_ACC(5);  // wait ds_ready
-        if (first && cur.n > 0 && !mbar_wait(&sm.dk_free, (cur.n - 1) & 1, ctx, kWAccFree)) break;
-        KB_ACC(6);  // wait dk_free
-        KB_FTR(1, g, 4);
-        tc_fence_after();
-        issue_acc(kColDK, kColDP, smem_u32(sm.q[g & 1]), first);
-        mma_commit(&sm.q_empty[g & 1]);
-        if (cur.last()) mma_commit(&sm.dk_done);
-        KB_FTR(1, g, 5);
-        KB_ACC(7);  // issue dK
-        if (!nxt.valid) break;
-        // dP(g+1)
-        if (!issue_dp(nxt)) break;
-        KB_ACC(8);  // dP(g+1) incl. waits for V, dO
-        cur = nxt;
-        cursor_next(a, nxt, n_items, n_ktiles);
-        KB_ACC(11);  // advancing the cursors
+        int cnt_next = 0;
+        for (int t = 0; ok && t < cnt; ++t, ++g) {
+          const bool first = t == 0, last = t == cnt - 1;
+          KB_FTR(1, g, 0);
+          KB_ACC(0);  // loop
+          // dV(g) += P(g) dO(g)
+          if (!mbar_wait(&sm.p_ready, g & 1, ctx, kWPReady)) { ok = false; break; }
+          KB_ACC(1);  // wait p_ready
+          // the first MMAs of an item overwrite dV / dK: the epilogue warps must have read the old ones
+          if (first && n > 0 && !mbar_wait(&sm.dv_free, (n - 1) & 1, ctx, kWAccFree)) { ok = false; break; }
+          KB_FTR(1, g, 1);
+          KB_ACC(2);  // wait dv_free
+          tc_fence_after();
+          issue_acc(kColDV, kColS, do_addr, first);
+          mma_commit(&sm.do_empty);
+          if (last) mma_commit(&sm.dv_done);  // the epilogue warps start on dV while dK(last) still runs
+          KB_FTR(1, g, 2);
+          KB_ACC(3);  // issue dV
+          // S(g+1): of this item, or the first of the next live one
+          if (last) {
+            item += gridDim.x;
+            cnt_next = next_live(item);
+          }
+          const bool more = !last || cnt_next > 0;
+          if (more && !issue_s(last ? n + 1 : n, g + 1, last)) { ok = false; break; }
+          KB_FTR(1, g, 3);
+          KB_ACC(4);  // S(g+1) incl. the look for the next item
+          // dK(g) += dS(g) Q(g)
+          if (!mbar_wait(&sm.ds_ready[g & 1], (g >> 1) & 1, ctx, kWDsReady)) { ok = false; break; }
+          KB_ACC(5);  // wait ds_ready
+          if (first && n > 0 && !mbar_wait(&sm.dk_free, (n - 1) & 1, ctx, kWAccFree)) { ok = false; break; }
+          KB_ACC(6);  // wait dk_free
+          KB_FTR(1, g, 4);
+          tc_fence_after();
+          issue_acc(kColDK, kColDP, smem_u32(sm.q[g & 1]), first);
+          mma_commit(&sm.q_empty[g & 1]);
+          if (last) mma_commit(&sm.dk_done);
+          KB_FTR(1, g, 5);
+          KB_ACC(7);  // issue dK
+          // dP(g+1)
+          if (more && !issue_dp(last ? n + 1 : n, g + 1, last, last ? cnt_next == 1 : t + 1 == cnt - 1)) { ok = false; break; }
+          KB_ACC(8);  // dP(g+1)
+        }
+        if (cnt_next == 0) break;
+        cnt = cnt_next;
+        ++n;
       }
 #ifdef KB_TRACE_FUSED
       if (blockIdx.x == 60)

@@ -40,6 +40,14 @@
 #include "sm100_host.h"
 
 namespace kb {
+#ifdef KB_TRACE_FWD
+// Debug build only: where the MMA thread and one softmax thread of CTA 60 spend their clocks; read back by
+// kb_debug_trace_fwd().  [0..15] MMA thread, [16..31] softmax thread (q tile A, row 0).
+__device__ long long g_fwtrace[32];
+#define KB_FACC(i) do { const long long tn_ = clock64(); acc_t[i] += tn_ - tl; tl = tn_; } while (0)
+#else
+#define KB_FACC(i) do { } while (0)
+#endif
 namespace {
 
 using namespace sm100;
@@ -47,7 +55,7 @@ using namespace sm100;
 constexpr int kBM = 128;  // rows of one q tile
 constexpr int kQTiles = 2;
 constexpr int kBN = 128;
-constexpr int kStagesK = 3, kStagesV = 2;
+constexpr int kStagesK = 2, kStagesV = 2;
 constexpr int kThreads = (kQTiles * 4 + 2) * 32;
 constexpr int kProducerWarp = kQTiles * 4, kMmaWarp = kQTiles * 4 + 1;
 constexpr uint32_t kTmemCols = 512;
@@ -70,6 +78,7 @@ struct alignas(1024) FwdSmem {
   uint8_t q[kQTiles][kBM * D * 2];
   uint8_t k[kStagesK][kBN * D * 2];
   uint8_t v[kStagesV][kBN * D * 2];
+  uint8_t o_stage[kQTiles][kBM * 128];  // one 64-column panel of a q tile's output on its way to a TMA store
   uint64_t q_full, k_full[kStagesK], k_empty[kStagesK], v_full[kStagesV], v_empty[kStagesV];
   uint64_t q_empty, s_ready[kQTiles], p_ready[kQTiles], o_done[kQTiles], o_free[kQTiles];
   uint32_t tmem_base;
@@ -151,7 +160,7 @@ __device__ __forceinline__ float softmax_block(uint32_t t_s, float scale, int k0
 template <int D, bool BF16>
 __global__ void __launch_bounds__(kThreads, 1)
 sa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                    const __grid_constant__ CUtensorMap tm_v, const FwdArgs a) {
+                    const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o, const FwdArgs a) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   FwdSmem<D>& sm = *reinterpret_cast<FwdSmem<D>*>(smem_raw);
 
@@ -273,10 +282,16 @@ sa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       int tiles_x[kQTiles] = {0, 0};    // S / P blocks of q tile x so far
       int items_x[kQTiles] = {0, 0};    // items in which q tile x was live so far
       bool ok = true;
+#ifdef KB_TRACE_FWD
+      long long acc_t[10] = {0};
+      long long tl = clock64();
+#endif
       for (int item = blockIdx.x; ok && item < n_items; item += gridDim.x) {
         const Item it = decode(item);
         if (!it.act[0] && !it.act[1]) continue;
+        KB_FACC(0);
         if (!mbar_wait(&sm.q_full, na & 1, ctx, kWaitQ)) break;
+        KB_FACC(1);
         // iteration t issues, per q tile x:  PV_x(t-1) then S_x(t)
         for (int t = it.u_begin; ok && t <= it.u_end; ++t) {
           const int i = t - it.u_begin;
@@ -288,8 +303,11 @@ sa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
               const int u = t - 1, vi = kbase + i - 1, sv = vi % kStagesV;
               const int lx = u - it.kr[x].begin;  // index within this q tile's range
               const int px = tiles_x[x] - 1;  // P block consumed now = last S block issued for x
+              KB_FACC(2);
               if (!mbar_wait(&sm.p_ready[x], px & 1, ctx, kWaitPReady)) { ok = false; break; }
+              KB_FACC(3 + x);
               if (!mbar_wait(&sm.v_full[sv], (vi / kStagesV) & 1, ctx, kWaitVFull)) { ok = false; break; }
+              KB_FACC(5);
               // the first P V of an item overwrites O: the softmax warps must have read the old one
               if (lx == 0 && items_x[x] > 0 && !mbar_wait(&sm.o_free[x], (items_x[x] - 1) & 1, ctx, kWaitOFree)) { ok = false; break; }
               tc_fence_after();
@@ -306,10 +324,13 @@ sa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
               const bool last_user = (x == kQTiles - 1) || !(u >= it.kr[1].begin && u < it.kr[1].end);
               if (last_user) mma_commit(&sm.v_empty[sv]);
               if (u == it.kr[x].end - 1) mma_commit(&sm.o_done[x]);
+              KB_FACC(6);
             }
             if (s_live) {
               const int ki = kbase + i, sk = ki % kStagesK;
+              KB_FACC(2);
               if (!mbar_wait(&sm.k_full[sk], (ki / kStagesK) & 1, ctx, kWaitKFull)) { ok = false; break; }
+              KB_FACC(7);
               tc_fence_after();
               uint32_t q_lo = desc_lo_kmajor(smem_u32(sm.q[x])), k_lo = desc_lo_kmajor(smem_u32(sm.k[sk]));
 #pragma unroll 1
@@ -321,6 +342,7 @@ sa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
               if (last_user) mma_commit(&sm.k_empty[sk]);
               mma_commit(&sm.s_ready[x]);
               ++tiles_x[x];
+              KB_FACC(8);
             }
           }
           if (t == it.u_end - 1) mma_commit(&sm.q_empty);  // every S of this item has been issued
@@ -330,6 +352,10 @@ sa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
 #pragma unroll
         for (int x = 0; x < kQTiles; ++x) items_x[x] += it.act[x] ? 1 : 0;
       }
+#ifdef KB_TRACE_FWD
+      if (blockIdx.x == 60)
+        for (int i = 0; i < 10; ++i) g_fwtrace[i] = acc_t[i];
+#endif
     }
   } else {
     // ------------------------------ softmax + epilogue ------------------------------
@@ -340,6 +366,10 @@ sa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     const float scale = a.scale_log2;
     int tiles = 0, items = 0;  // S blocks / live items of this q tile so far
     bool ok = true;
+#ifdef KB_TRACE_FWD
+    long long acc_t[8] = {0};
+    long long tl = clock64();
+#endif
     for (int item = blockIdx.x; ok && item < n_items; item += gridDim.x) {
       const Item it = decode(item);
       const int qi = it.q0 + x * kBM + row;
@@ -368,9 +398,11 @@ sa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
 
       for (int lx = 0; lx < n_tiles; ++lx, ++tiles) {
         const int k0 = (it.kr[x].begin + lx) * kBN;
+        KB_FACC(0);
         ok = __all_sync(0xffffffffu, mbar_wait(&sm.s_ready[x], tiles & 1, ctx, kWaitSReady));
         if (!ok) break;
         tc_fence_after();
+        KB_FACC(1);
         const bool warp_full = __all_sync(0xffffffffu, lo <= k0 && k0 + kBN <= hi);
         bool need;
         float alpha;
@@ -378,6 +410,7 @@ sa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
           alpha = softmax_block<BF16, false>(t_s, scale, k0, lo, hi, m_used, l, need);
         else
           alpha = softmax_block<BF16, true>(t_s, scale, k0, lo, hi, m_used, l, need);
+        KB_FACC(2);
         if (lx > 0 && __any_sync(0xffffffffu, need)) {
           // S(lx) is complete, so the P V of the previous tile (issued before it) is too: O is idle
 #pragma unroll
@@ -390,14 +423,18 @@ sa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
             tmem_st32(t_o + cc * 32, r);
           }
         }
+        KB_FACC(3);
         tmem_wait_st();
         tc_fence_before();
         mbar_arrive(&sm.p_ready[x]);
+        KB_FACC(4);
       }
       if (!ok) break;
+      KB_FACC(0);
 
       ok = __all_sync(0xffffffffu, mbar_wait(&sm.o_done[x], items & 1, ctx, kWaitEpilogue));
       if (!ok) break;
+      KB_FACC(5);
       ++items;
       tc_fence_after();
       // pull the whole O row out of TMEM, release the accumulator to the next item, then store
@@ -409,20 +446,40 @@ sa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       mbar_arrive(&sm.o_free[x]);
       const bool valid = qi < it.len;
       const float inv = valid ? 1.f / l : 0.f;
-      if (qi < T) {
-        uint4* dst = reinterpret_cast<uint4*>(o_row);
+      // The rows leave through shared memory and a TMA store, one 64-column panel at a time (row = 128
+      // bytes, 128-byte swizzle).  Plain 16-byte stores of a 256-byte row per thread touch 32 different
+      // lines per instruction and held the softmax warps for several thousand clocks per item.  Rows past
+      // the end of the tensor are clipped by the store; rows past `len` are zeros (inv = 0).
+      uint8_t* stage = sm.o_stage[x] + row * 128;
 #pragma unroll
-        for (int g = 0; g < D / 8; ++g) {
+      for (int p = 0; p < kPanels; ++p) {
+        if (row == 0) tma_store_wait_read();  // the store that used the buffer last has read it
+        named_barrier_sync(1 + x, kBM);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int e = p * 64 + 8 * j;
           uint4 w;
-          w.x = pack16x2<BF16>(__uint_as_float(r[8 * g + 0]) * inv, __uint_as_float(r[8 * g + 1]) * inv);
-          w.y = pack16x2<BF16>(__uint_as_float(r[8 * g + 2]) * inv, __uint_as_float(r[8 * g + 3]) * inv);
-          w.z = pack16x2<BF16>(__uint_as_float(r[8 * g + 4]) * inv, __uint_as_float(r[8 * g + 5]) * inv);
-          w.w = pack16x2<BF16>(__uint_as_float(r[8 * g + 6]) * inv, __uint_as_float(r[8 * g + 7]) * inv);
-          dst[g] = w;
+          w.x = pack16x2<BF16>(__uint_as_float(r[e + 0]) * inv, __uint_as_float(r[e + 1]) * inv);
+          w.y = pack16x2<BF16>(__uint_as_float(r[e + 2]) * inv, __uint_as_float(r[e + 3]) * inv);
+          w.z = pack16x2<BF16>(__uint_as_float(r[e + 4]) * inv, __uint_as_float(r[e + 5]) * inv);
+          w.w = pack16x2<BF16>(__uint_as_float(r[e + 6]) * inv, __uint_as_float(r[e + 7]) * inv);
+          *reinterpret_cast<uint4*>(stage + ((j ^ (row & 7)) << 4)) = w;
         }
-        if (lse_row) *lse_row = valid ? m_used + log2f(l) : 0.f;
+        fence_proxy_async();  // the store reads shared memory through the async proxy
+        named_barrier_sync(1 + x, kBM);
+        if (row == 0) {
+          tma_store_4d(&tm_o, sm.o_stage[x], p * 64, it.q0 + x * kBM, it.h, it.b);
+          tma_store_commit();
+        }
       }
+      if (qi < T && lse_row) *lse_row = valid ? m_used + log2f(l) : 0.f;
+      KB_FACC(6);
     }
+    if (row == 0) tma_store_wait_all();
+#ifdef KB_TRACE_FWD
+    if (blockIdx.x == 60 && threadIdx.x == 0)
+      for (int i = 0; i < 8; ++i) g_fwtrace[16 + i] = acc_t[i];
+#endif
   }
 
   tc_fence_before();
@@ -435,10 +492,10 @@ sa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
 
 template <int D, bool BF16>
 int launch(const kb_sa_fwd_params& p, int32_t c, int32_t back, cudaStream_t s) {
-  CUtensorMap tm_q, tm_k, tm_v;
+  CUtensorMap tm_q, tm_k, tm_v, tm_o;
   const int32_t H_kv = p.H_kv > 0 ? p.H_kv : p.H;
   if (!make_tile_map_4d(&tm_q, p.q, p.B, p.H, p.T, D, kBM) || !make_tile_map_4d(&tm_k, p.k, p.B, H_kv, p.T, D, kBN) ||
-      !make_tile_map_4d(&tm_v, p.v, p.B, H_kv, p.T, D, kBN))
+      !make_tile_map_4d(&tm_v, p.v, p.B, H_kv, p.T, D, kBN) || !make_tile_map_4d_contiguous(&tm_o, p.o, p.B, p.H, p.T, D, kBM))
     return KB_ERR_UNSUPPORTED;
   auto kern = sa_fwd_sm100_kernel<D, BF16>;
   constexpr size_t smem = sizeof(FwdSmem<D>);
@@ -466,7 +523,7 @@ int launch(const kb_sa_fwd_params& p, int32_t c, int32_t back, cudaStream_t s) {
   KB_CUDA_TRY(cudaGetDevice(&dev));
   KB_CUDA_TRY(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev));
   const unsigned grid = (unsigned)(n_items < n_sm ? n_items : n_sm);  // persistent: one CTA per SM
-  kern<<<grid, kThreads, smem, s>>>(tm_q, tm_k, tm_v, a);
+  kern<<<grid, kThreads, smem, s>>>(tm_q, tm_k, tm_v, tm_o, a);
   KB_LAUNCH_CHECK("sa_fwd_sm100_kernel");
   return KB_OK;
 }
@@ -482,3 +539,9 @@ int sa_fwd_sm100(const kb_sa_fwd_params& p, int32_t c, int32_t back, cudaStream_
 }
 
 }  // namespace kb
+
+#ifdef KB_TRACE_FWD
+extern "C" __attribute__((visibility("default"))) int kb_debug_trace_fwd(long long* out) {
+  return (int)cudaMemcpyFromSymbol(out, kb::g_fwtrace, sizeof(kb::g_fwtrace));
+}
+#endif
