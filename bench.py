@@ -62,7 +62,7 @@ TORCH_DTYPES = {"bf16": torch.bfloat16, "f16": torch.float16, "f32": torch.float
 # Traffic is proportional to the number of slices: every slice reads Q, K, V, dO once and writes dK, dV once
 # (two-pass dK/dV pass: 782 MB), plus, in the single-evaluation main kernel, its 16-bit dS tiles (1 624 MB).
 NCU_TRAFFIC_PER_SLICE = {"bwd_dkdv_pass": {"cfg3": 782e6 / 32, "prof": 782e6 / 32},
-                         "bwd_main": {"cfg3": 1624e6 / 32, "prof": 1624e6 / 32}}
+                         "bwd_main": {"cfg3": 1556e6 / 32, "prof": 1556e6 / 32}}
 
 
 def _peaks():

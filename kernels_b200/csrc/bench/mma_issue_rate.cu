@@ -1,8 +1,12 @@
-// Microbenchmark behind the tile table: SM clocks per tcgen05.mma instruction (M = 128, K = 16, bf16 in,
-// fp32 out) when one thread of every SM issues them back to back, for A from shared memory (SS) or TMEM
-// (TS), N = 64 / 128 / 256, one accumulator or several in rotation, with and without other warps loading
-// TMEM, computing exponentials and reading / writing shared memory.  Operands are whatever the memory
-// holds: only timing is measured.  Stand-alone (no torch); every wait is bounded.
+// Microbenchmark behind the kernels' MMA issue loops: SM clocks per tcgen05.mma instruction (M = 128, K = 16,
+// bf16 in, fp32 out) when one thread of every SM issues them back to back.  Two things are measured apart:
+//   * what the ISSUING THREAD costs: the same instruction stream written four ways (descriptors rebuilt from a
+//     runtime loop counter; fully unrolled; descriptor low words stepped by adds, four instructions per loop
+//     trip; the whole warp converged with one elected lane) at N = 16, where the tensor pipe is almost free;
+//   * what the TENSOR PIPE costs: N = 64 / 128 / 256 with the cheapest issue form, A from shared memory (SS)
+//     or from TMEM (TS), alone and with eight other warps loading / storing TMEM, storing / loading shared
+//     memory and computing exponentials.
+// Operands are whatever the memory holds: only timing is measured.  Stand-alone (no torch); every wait is bounded.
 // Build and run:
 //   nvcc -gencode arch=compute_100a,code=sm_100a -O3 -std=c++17 -I include -I kernels_b200/csrc -o mma_issue_rate kernels_b200/csrc/bench/mma_issue_rate.cu
 #include <cstdio>
@@ -11,9 +15,18 @@
 #include "../sm100_ptx.cuh"
 using namespace kb::sm100;
 
-// mode bits: 1 = TS (A from TMEM) else SS; 2 = N256 (else N128); 4 = noise: 8 warps tcgen05.ld; 8 = noise: 8 warps ex2/fma loops;
-// 16 = noise: 8 warps st.shared; 32 = noise: 8 warps ld.shared broadcast; 64 = N64; 128 = commit after every 8 instrs + wait (dependency)
-__global__ void __launch_bounds__(320, 1) k(int mode, int iters, long long* out) {
+__device__ __forceinline__ void mma_ss_lo_pred(uint32_t d, uint32_t a_lo, uint32_t b_lo, uint32_t idesc, uint32_t go) {
+  asm volatile(
+      "{\n\t.reg .pred q;\n\t.reg .b64 da, db;\n\tsetp.ne.b32 q, %4, 0;\n\tmov.b64 da, {%1, %5};\n\tmov.b64 db, {%2, %5};\n\t"
+      "@q tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, 1;\n\t}" ::"r"(d), "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(go),
+      "r"(kDescHiSw128)
+      : "memory");
+}
+
+enum Form { kRolled = 0, kUnrolled = 1, kLowWords4 = 2, kConverged = 3 };
+// noise bits (warps 0-7): 1 tcgen05.ld, 2 tcgen05.st, 4 st.shared, 8 ld.shared, 16 ex2 + fma
+template <int FORM, int N, bool TS>
+__global__ void __launch_bounds__(320, 1) k(int iters, long long* out, int noise) {
   extern __shared__ __align__(1024) uint8_t smem[];
   __shared__ uint64_t bar;
   __shared__ uint32_t tmem_base;
@@ -25,67 +38,74 @@ __global__ void __launch_bounds__(320, 1) k(int mode, int iters, long long* out)
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = tmem_base;
-  const int N = (mode & 2) ? 256 : ((mode & 64) ? 64 : 128);
   if (warp == 9) {
-    if (lane == 0) {
-      const uint32_t idesc_ss = make_idesc(true, 128, N, false, false);
-      const uint32_t idesc_ts = make_idesc(true, 128, N, false, true);
-      const uint32_t a_addr = smem_u32(smem), b_addr = smem_u32(smem + 65536);
-      long long t0 = clock64();
-      int ph = 0;
+    constexpr uint32_t idesc = make_idesc(true, 128, N, false, TS);
+    const uint32_t a_addr = smem_u32(smem), b_addr = smem_u32(smem + 32768);
+    const uint32_t a_lo = desc_lo_kmajor(a_addr), b_lo = desc_lo_kmajor(b_addr), bm_lo = desc_lo_mnmajor(b_addr, 16384);
+    const bool leader = FORM == kConverged ? elect_one() : lane == 0;
+    if (FORM == kConverged || lane == 0) {
+      const long long t0 = clock64();
       for (int it = 0; it < iters; ++it) {
+        if (FORM == kRolled) {
+#pragma unroll 1
+          for (int kk = 0; kk < 8; ++kk) {
+            const uint32_t off = (kk / 4) * 16384 + (kk % 4) * 32;
+            mma_ss(tmem + 256, desc_kmajor(a_addr + off), desc_kmajor(b_addr + off), idesc, kk > 0);
+          }
+        } else if (FORM == kUnrolled) {
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
-          const uint32_t off = (kk / 4) * 16384 + (kk % 4) * 32;
-          const uint32_t dcol = (mode & 256) ? ((kk & 1) ? 384u : 256u) : ((mode & 512) ? (uint32_t)((kk & 3) * 128) : 256u);
-          if (mode & 1)
-            mma_ts(tmem + dcol, tmem + (kk / 4) * 64 + (kk % 4) * 8, desc_mnmajor(b_addr + kk * 2048, 16384), idesc_ts, true);
-          else
-            mma_ss(tmem + dcol, desc_kmajor(a_addr + off), desc_kmajor(b_addr + off), idesc_ss, true);
-        }
-        if (mode & 128) {
-          mma_commit(&bar);
-          for (int spin = 0; spin < (1 << 22) && !mbar_try_wait(&bar, ph); ++spin) {}
-          ph ^= 1;
+          for (int kk = 0; kk < 8; ++kk) {
+            if (TS)
+              mma_ts_lo(tmem + 256, tmem + (kk / 4) * 64 + (kk % 4) * 8, bm_lo + kk * 128, idesc, true);
+            else
+              mma_ss_lo(tmem + 256, a_lo + (kk / 4) * 1024 + (kk % 4) * 2, b_lo + (kk / 4) * 1024 + (kk % 4) * 2, idesc, true);
+          }
+        } else if (FORM == kLowWords4) {
+#pragma unroll 1
+          for (int p = 0; p < 2; ++p) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) mma_ss_lo(tmem + 256, a_lo + p * 1024 + 2 * i, b_lo + p * 1024 + 2 * i, idesc, p > 0 || i > 0);
+          }
+        } else {
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk)
+            mma_ss_lo_pred(tmem + 256, a_lo + (kk / 4) * 1024 + (kk % 4) * 2, b_lo + (kk / 4) * 1024 + (kk % 4) * 2, idesc, leader);
         }
       }
-      long long t1 = clock64();
-      mma_commit(&bar);
-      for (int spin = 0; spin < (1 << 24) && !mbar_try_wait(&bar, (mode & 128) ? ph : 0); ++spin) {}
-      long long t2 = clock64();
-      out[0] = t1 - t0;
-      out[1] = t2 - t0;
-      stop = 1;
+      const long long t1 = clock64();
+      if (leader) mma_commit(&bar);
+      if (FORM == kConverged) __syncwarp();
+      for (int spin = 0; spin < (1 << 24) && !mbar_try_wait(&bar, 0); ++spin) {}
+      const long long t2 = clock64();
+      if (blockIdx.x == 0 && leader) { out[0] = t1 - t0; out[1] = t2 - t0; }
+      if (leader) stop = 1;
     }
   } else if (warp < 8) {
     const uint32_t t_lane = tmem + ((uint32_t)((warp & 3) * 32) << 16);
     float acc = 0.f;
     uint32_t r[32];
     for (int i = 0; i < 32; ++i) r[i] = i + lane;
-    for (int round = 0; round < (1 << 22) && !stop; ++round) {
-      if (mode & 4) {
-        tmem_ld32(t_lane + (warp >> 2) * 64, r);
-        tmem_wait_ld();
-        acc += __uint_as_float(r[5]);
-      }
-      if (mode & 8) {
-#pragma unroll
-        for (int i = 0; i < 32; ++i) acc += ex2_approx(fmaf(__uint_as_float(r[i]), 1.0001f, acc));
-      }
-      if (mode & 16) {
+    for (int round = 0; round < (1 << 22) && !stop && noise; ++round) {
+      if (noise & 1) { tmem_ld32(t_lane + (warp >> 2) * 64, r); tmem_wait_ld(); acc += __uint_as_float(r[5]); }
+      if (noise & 2) { tmem_st32(t_lane + 128 + (warp >> 2) * 64, r); tmem_wait_st(); }
+      if (noise & 4) {
 #pragma unroll
         for (int i = 0; i < 8; ++i)
-          *reinterpret_cast<uint4*>(smem + 131072 + (warp * 32 + lane) * 128 + ((i ^ (lane & 7)) << 4)) = make_uint4(r[0], r[1], r[2], r[3]);
+          *reinterpret_cast<uint4*>(smem + 65536 + (warp * 32 + lane) * 128 + ((i ^ (lane & 7)) << 4)) = make_uint4(r[0], r[1], r[2], r[3]);
       }
-      if (mode & 32) {
+      if (noise & 8) {
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          float4 v;
-          asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(smem_u32(smem + 131072 + 65536 + i * 16 + (warp & 1) * 256)));
-          acc += v.x;
+        for (int i = 0; i < 8; ++i) {
+          uint32_t vx, vy, vz, vw;
+          asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(vx), "=r"(vy), "=r"(vz), "=r"(vw)
+                       : "r"(smem_u32(smem + 98304 + (warp * 32 + lane) * 128 + ((i ^ (lane & 7)) << 4))));
+          r[i] ^= vx;
         }
       }
-      if (!(mode & 60)) __nanosleep(200);
+      if (noise & 16) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(ex2_approx(fmaf(__uint_as_float(r[i]), 1.0001f, acc)));
+      }
     }
     if (acc == 123.456f) out[7] = 1;
   }
@@ -94,23 +114,39 @@ __global__ void __launch_bounds__(320, 1) k(int mode, int iters, long long* out)
   if (warp == 9) tmem_dealloc(tmem, 512);
 }
 
+template <int FORM, int N, bool TS>
+void run(long long* d, int noise, const char* what) {
+  cudaFuncSetAttribute(k<FORM, N, TS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+  const int iters = 1024;
+  for (int rep = 0; rep < 2; ++rep) {
+    k<FORM, N, TS><<<148, 320, 200 * 1024>>>(iters, d, noise);
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) { printf("%s\n", cudaGetErrorString(e)); exit(1); }
+  }
+  long long h[2];
+  cudaMemcpy(h, d, 16, cudaMemcpyDeviceToHost);
+  printf("%-34s %s N=%3d noise %2d: issue %6.1f  complete %6.1f clk/instruction\n", what, TS ? "TS" : "SS", N, noise, h[0] / (8.0 * iters),
+         h[1] / (8.0 * iters));
+}
+
 int main() {
   long long* d;
   cudaMalloc(&d, 64);
-  cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-  const int iters = 2000;
-  int modes[] = {0, 1, 2, 3, 64, 128, 129, 256, 257, 512, 513, 256 + 64, 512 + 64, 4, 5, 8, 9, 16, 17, 32, 33, 60, 61, 256 + 60, 257 + 60};
-  for (int m : modes) {
-    for (int rep = 0; rep < 2; ++rep) {
-      k<<<148, 320, 200 * 1024>>>(m, iters, d);
-      cudaError_t e = cudaDeviceSynchronize();
-      if (e != cudaSuccess) { printf("mode %d: %s\n", m, cudaGetErrorString(e)); return 1; }
-    }
-    long long h[2];
-    cudaMemcpy(h, d, 16, cudaMemcpyDeviceToHost);
-    printf("mode %3d (%s N%d%s%s%s%s%s%s): issue %.1f clk/instr, complete %.1f clk/instr\n", m, (m & 1) ? "TS" : "SS",
-           (m & 2) ? 256 : ((m & 64) ? 64 : 128), (m & 128) ? " dep8" : "", (m & 4) ? " +tmem_ld" : "", (m & 8) ? " +ex2" : "",
-           (m & 16) ? " +st.shared" : "", (m & 32) ? " +ld.shared" : "", (m & 256) ? " 2acc" : ((m & 512) ? " 4acc" : ""), h[0] / (8.0 * iters), h[1] / (8.0 * iters));
+  run<kRolled, 16, false>(d, 0, "rolled, descriptors per trip");
+  run<kUnrolled, 16, false>(d, 0, "unrolled, low words");
+  run<kLowWords4, 16, false>(d, 0, "low words, 4 per trip");
+  run<kConverged, 16, false>(d, 0, "converged warp, elected lane");
+  run<kRolled, 128, false>(d, 0, "rolled, descriptors per trip");
+  run<kLowWords4, 128, false>(d, 0, "low words, 4 per trip");
+  run<kLowWords4, 128, false>(d, 16, "low words, 4 per trip");
+  run<kUnrolled, 64, false>(d, 0, "unrolled, low words");
+  run<kUnrolled, 128, false>(d, 0, "unrolled, low words");
+  run<kUnrolled, 128, true>(d, 0, "unrolled, low words");
+  run<kUnrolled, 256, false>(d, 0, "unrolled, low words");
+  run<kUnrolled, 256, true>(d, 0, "unrolled, low words");
+  for (int noise : {1, 2, 4, 8, 16, 31}) {
+    run<kUnrolled, 128, false>(d, noise, "unrolled, low words");
+    run<kUnrolled, 128, true>(d, noise, "unrolled, low words");
   }
   return 0;
 }

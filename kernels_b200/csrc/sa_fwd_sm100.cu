@@ -3,7 +3,7 @@
 // One CTA owns TWO tiles of 128 query rows (A and B, 256 consecutive rows) of one (batch, head)
 // and walks the live KV tiles (128 keys each) of the streaming schedule (schedule.h); both
 // q tiles use every K/V tile that is brought into shared memory, which halves the L2 traffic
-// per FLOP against one q tile per CTA.  Ten warps, three roles:
+// per FLOP against one q tile per CTA.  Ten warps, three roles (K and V rings two deep; output rows leave through shared memory and TMA stores):
 //   warps 0-3 / 4-7  softmax of q tile A / B: thread r owns query row r of its tile (= TMEM lane
 //              r).  Reads a 128 x 128 block of S from TMEM into registers, keeps the running
 //              max / sum, writes P (16-bit) back over S, rescales O when the max moved by more
