@@ -97,6 +97,12 @@ typedef struct kb_sa_fwd_params {
    * tcgen05 kernels take H_kv != H; other calls return KB_ERR_UNSUPPORTED with nothing launched (the caller
    * then repeats the K/V heads itself). */
   int32_t H_kv;
+  /* Output layout (an extension: the reference allocates its outputs itself, kernel.py:1304-1308).  All
+   * zeros: `o` is [B,H,T,D] and `lse` [B,H,T], contiguous.  Otherwise the element strides of o's b, h, t
+   * axes (d has stride 1; multiples of 8 elements) and of lse's b, h axes (t has stride 1).  Only the
+   * tcgen05 kernels take a strided output; other calls return KB_ERR_UNSUPPORTED with nothing launched. */
+  int64_t o_stride[3];
+  int64_t lse_stride[2];
 } kb_sa_fwd_params;
 
 KB_API int kb_sa_fwd(const kb_sa_fwd_params* p, void* stream);
@@ -139,6 +145,11 @@ typedef struct kb_sa_bwd_params {
    * contributions of the H / H_kv query heads of a group (in a fixed order: still bitwise repeatable).
    * Only the single-evaluation tcgen05 kernels take H_kv != H. */
   int32_t H_kv;
+  /* Layout of dq, of dk and dv, and of lse, as o_stride / lse_stride of kb_sa_fwd_params (all zeros:
+   * contiguous).  Only the single-evaluation tcgen05 kernels take strided gradients. */
+  int64_t dq_stride[3];
+  int64_t dkv_stride[3];
+  int64_t lse_stride[2];
 } kb_sa_bwd_params;
 
 KB_API int kb_sa_bwd(const kb_sa_bwd_params* p, void* stream);
@@ -168,6 +179,42 @@ KB_API uint64_t kb_sa_bwd_workspace_bytes(int32_t B, int32_t H, int32_t T, int32
  */
 #define KB_NOALLOC_MAX_ROWS (1 << 21)
 KB_API int kb_sa_bwd_noalloc(const kb_sa_bwd_params* p, void* stream);
+
+/*
+ * Streaming attention over a PACKED batch (no counterpart in the reference, whose callers hold padded
+ * [B, T] batches with `lens`, kernel.py:1586-1652): the sequences lie one after the other along the token
+ * axis, q / o / dq as [total, H, D], k / v / dk / dv as [total, H_kv, D], lse as [H, total]; sequence b owns
+ * the rows [cu_seqlens[b], cu_seqlens[b + 1]).  No padded row is read, computed or written.  Each sequence is
+ * one launch of the kernels above over a strided view (batch 1, T = its length, tiles counted from its own
+ * first row), so the results equal those of the padded call row for row.  `cu_seqlens` is read on the HOST.
+ * tcgen05 kernels only (f16 / bf16, D 64 or 128); the backward needs `delta_ws` (H * max_len floats) and
+ * `ds_ws` (kb_sa_bwd_workspace_bytes(1, H, max_len, ...) bytes), both reused from sequence to sequence.
+ */
+typedef struct kb_sa_varlen_params {
+  const void* q;
+  const void* k;
+  const void* v;
+  void* o;
+  float* lse;      /* forward: written (may be NULL); backward: read */
+  const void* d_o; /* backward only, [total, H, D] */
+  void* dq;
+  void* dk;
+  void* dv;
+  float* delta_ws;
+  void* ds_ws;
+  uint64_t ds_ws_bytes;
+  const int32_t* cu_seqlens; /* host memory, B + 1 non-decreasing entries, cu_seqlens[0] = 0 */
+  int32_t B, H, H_kv, D;
+  int32_t dtype;
+  int32_t context_size;
+  int32_t back_contexts;
+  float sm_scale;
+  uint32_t flags;
+  int32_t* status;
+} kb_sa_varlen_params;
+
+KB_API int kb_sa_fwd_varlen(const kb_sa_varlen_params* p, void* stream);
+KB_API int kb_sa_bwd_varlen(const kb_sa_varlen_params* p, void* stream);
 
 /*
  * Dense (non-causal) self-attention forward with key padding by `lens`.

@@ -25,7 +25,7 @@ KB_NOALLOC_MAX_ROWS = 1 << 21
 _DTYPES = {torch.float32: KB_F32, torch.float16: KB_F16, torch.bfloat16: KB_BF16}
 
 EXPORTS = (
-    "kb_sa_fwd", "kb_sa_bwd", "kb_sa_bwd_workspace_bytes", "kb_sa_bwd_noalloc", "kb_fa_fwd", "kb_softmax_fwd", "kb_sa_plan", "kb_sa_tile_config",
+    "kb_sa_fwd", "kb_sa_bwd", "kb_sa_bwd_workspace_bytes", "kb_sa_bwd_noalloc", "kb_sa_fwd_varlen", "kb_sa_bwd_varlen", "kb_fa_fwd", "kb_softmax_fwd", "kb_sa_plan", "kb_sa_tile_config",
     "kb_launch_count", "kb_strerror", "kb_last_cuda_error", "kb_version",
 )
 
@@ -43,6 +43,7 @@ class SaFwdParams(C.Structure):
         ("dtype", C.c_int32), ("context_size", C.c_int32), ("back_contexts", C.c_int32),
         ("sm_scale", C.c_float), ("flags", C.c_uint32), ("status", C.c_void_p),
         ("H_kv", C.c_int32),
+        ("o_stride", C.c_int64 * 3), ("lse_stride", C.c_int64 * 2),
     ]
 
 
@@ -57,6 +58,20 @@ class SaBwdParams(C.Structure):
         ("sm_scale", C.c_float), ("flags", C.c_uint32), ("status", C.c_void_p),
         ("ds_ws", C.c_void_p), ("ds_ws_bytes", C.c_uint64),
         ("H_kv", C.c_int32),
+        ("dq_stride", C.c_int64 * 3), ("dkv_stride", C.c_int64 * 3), ("lse_stride", C.c_int64 * 2),
+    ]
+
+
+class SaVarlenParams(C.Structure):
+    """kb_sa_varlen_params: a packed batch, sequences one after the other along the token axis."""
+    _fields_ = [
+        ("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("o", C.c_void_p), ("lse", C.c_void_p),
+        ("d_o", C.c_void_p), ("dq", C.c_void_p), ("dk", C.c_void_p), ("dv", C.c_void_p),
+        ("delta_ws", C.c_void_p), ("ds_ws", C.c_void_p), ("ds_ws_bytes", C.c_uint64),
+        ("cu_seqlens", C.c_void_p),
+        ("B", C.c_int32), ("H", C.c_int32), ("H_kv", C.c_int32), ("D", C.c_int32),
+        ("dtype", C.c_int32), ("context_size", C.c_int32), ("back_contexts", C.c_int32),
+        ("sm_scale", C.c_float), ("flags", C.c_uint32), ("status", C.c_void_p),
     ]
 
 
@@ -86,6 +101,9 @@ def load() -> C.CDLL:
     lib.kb_sa_bwd.argtypes = [C.POINTER(SaBwdParams), C.c_void_p]
     lib.kb_sa_bwd_noalloc.argtypes = [C.POINTER(SaBwdParams), C.c_void_p]
     lib.kb_sa_bwd_noalloc.restype = C.c_int
+    lib.kb_sa_fwd_varlen.argtypes = [C.POINTER(SaVarlenParams), C.c_void_p]
+    lib.kb_sa_bwd_varlen.argtypes = [C.POINTER(SaVarlenParams), C.c_void_p]
+    lib.kb_sa_fwd_varlen.restype = lib.kb_sa_bwd_varlen.restype = C.c_int
     lib.kb_sa_bwd_workspace_bytes.argtypes = [C.c_int32] * 7
     lib.kb_sa_bwd_workspace_bytes.restype = C.c_uint64
     lib.kb_softmax_fwd.argtypes = [C.POINTER(SoftmaxParams), C.c_void_p]

@@ -75,6 +75,20 @@ int32_t kv_heads(const P* p) {
   return p->H_kv;
 }
 
+template <int N>
+bool any_stride(const int64_t (&st)[N]) {
+  for (int i = 0; i < N; ++i)
+    if (st[i]) return true;
+  return false;
+}
+// a strided output: 16-byte aligned rows (the tensor map's and the plain stores' requirement)
+bool out_stride_ok(const int64_t (&st)[3]) {
+  if (!any_stride(st)) return true;
+  for (int i = 0; i < 3; ++i)
+    if (st[i] < 0 || st[i] % 8) return false;
+  return st[2] > 0;
+}
+
 int run_fwd(const kb_sa_fwd_params* p, void* stream, bool dense) {
   int rc = check_common(p);
   if (rc) return rc;
@@ -82,6 +96,8 @@ int run_fwd(const kb_sa_fwd_params* p, void* stream, bool dense) {
   if (!dense && (p->context_size < 1 || p->back_contexts < 0)) return KB_ERR_BAD_ARGUMENT;
   if (empty(p->B, p->H, p->T)) return KB_OK;
   if (!p->q.data || !p->k.data || !p->v.data || !p->o) return KB_ERR_BAD_ARGUMENT;
+  if (!out_stride_ok(p->o_stride) || p->lse_stride[0] < 0 || p->lse_stride[1] < 0) return KB_ERR_BAD_ARGUMENT;
+  const bool strided_out = any_stride(p->o_stride) || any_stride(p->lse_stride);
   const int32_t c = dense ? kb_max_i32(p->T, 1) : kb_clamp_context(p->context_size, p->T);
   const int32_t back = dense ? 0 : kb_clamp_back(p->back_contexts, p->T, c);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
@@ -93,7 +109,8 @@ int run_fwd(const kb_sa_fwd_params* p, void* stream, bool dense) {
     if (rc != KB_ERR_UNSUPPORTED) return rc;
   }
 #endif
-  if (kv_heads(p) != p->H) return KB_ERR_UNSUPPORTED;  // the generic kernels want one K/V head per query head
+  // the generic kernels want one K/V head per query head and contiguous outputs
+  if (kv_heads(p) != p->H || strided_out) return KB_ERR_UNSUPPORTED;
   return sa_fwd_generic(*p, c, back, s);
 }
 
@@ -114,6 +131,9 @@ int kb_sa_bwd(const kb_sa_bwd_params* p, void* stream) {
   if (!p->q.data || !p->k.data || !p->v.data || !p->o.data || !p->d_o.data || !p->lse || !p->dq || !p->dk ||
       !p->dv || !p->delta_ws)
     return KB_ERR_BAD_ARGUMENT;
+  if (!kb::out_stride_ok(p->dq_stride) || !kb::out_stride_ok(p->dkv_stride) || p->lse_stride[0] < 0 || p->lse_stride[1] < 0)
+    return KB_ERR_BAD_ARGUMENT;
+  const bool strided_out = kb::any_stride(p->dq_stride) || kb::any_stride(p->dkv_stride) || kb::any_stride(p->lse_stride);
   const int32_t c = kb_clamp_context(p->context_size, p->T);
   const int32_t back = kb_clamp_back(p->back_contexts, p->T, c);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
@@ -126,13 +146,100 @@ int kb_sa_bwd(const kb_sa_bwd_params* p, void* stream) {
       if (rc != KB_ERR_UNSUPPORTED) return rc;
     }
 #endif
-    if (kb::kv_heads(p) != p->H) return KB_ERR_UNSUPPORTED;  // shared K/V heads: single-evaluation kernels only
+    // shared K/V heads and strided gradients: single-evaluation kernels only
+    if (kb::kv_heads(p) != p->H || strided_out) return KB_ERR_UNSUPPORTED;
     const int rc = kb::sa_bwd_sm100(*p, c, back, s);
     if (rc != KB_ERR_UNSUPPORTED) return rc;
   }
 #endif
-  if (kb::kv_heads(p) != p->H) return KB_ERR_UNSUPPORTED;
+  if (kb::kv_heads(p) != p->H || strided_out) return KB_ERR_UNSUPPORTED;
   return kb::sa_bwd_generic(*p, c, back, s);
+}
+
+// Packed batch: one call of the entry points above per sequence, over strided views of the packed tensors.
+namespace {
+int check_varlen(const kb_sa_varlen_params* p, bool backward) {
+  if (!p || p->B < 0 || p->H < 1 || p->context_size < 1 || p->back_contexts < 0) return KB_ERR_BAD_ARGUMENT;
+  const int32_t Hk = p->H_kv > 0 ? p->H_kv : p->H;
+  if (Hk > p->H || p->H % Hk) return KB_ERR_BAD_ARGUMENT;
+  if (!kb::sm100_shape_ok(p->dtype, p->D, p->flags)) return KB_ERR_UNSUPPORTED;
+  if (p->B == 0) return KB_OK;
+  if (!p->cu_seqlens || p->cu_seqlens[0] != 0) return KB_ERR_BAD_ARGUMENT;
+  for (int32_t b = 0; b < p->B; ++b)
+    if (p->cu_seqlens[b + 1] < p->cu_seqlens[b]) return KB_ERR_BAD_ARGUMENT;
+  if (p->cu_seqlens[p->B] == 0) return KB_OK;
+  if (!p->q || !p->k || !p->v || !p->o) return KB_ERR_BAD_ARGUMENT;
+  if (backward && (!p->lse || !p->d_o || !p->dq || !p->dk || !p->dv || !p->delta_ws || !p->ds_ws)) return KB_ERR_BAD_ARGUMENT;
+  return KB_OK;
+}
+// rows [row0, ...) of a packed [total, heads, D] tensor as a [1, heads, len, D] view
+kb_tensor4 packed_view(const void* base, int64_t row0, int32_t heads, int32_t D) {
+  kb_tensor4 t;
+  t.data = static_cast<const uint16_t*>(base) + row0 * heads * D;
+  t.stride[0] = 0;  // extent 1
+  t.stride[1] = D;
+  t.stride[2] = (int64_t)heads * D;
+  t.stride[3] = 1;
+  return t;
+}
+}  // namespace
+
+int kb_sa_fwd_varlen(const kb_sa_varlen_params* p, void* stream) {
+  int rc = check_varlen(p, false);
+  if (rc || p->B == 0) return rc;
+  const int32_t Hk = p->H_kv > 0 ? p->H_kv : p->H, D = p->D;
+  const int64_t total = p->cu_seqlens[p->B];
+  for (int32_t b = 0; b < p->B; ++b) {
+    const int64_t r0 = p->cu_seqlens[b];
+    const int32_t len = p->cu_seqlens[b + 1] - p->cu_seqlens[b];
+    if (len == 0) continue;
+    kb_sa_fwd_params f = {};
+    f.q = packed_view(p->q, r0, p->H, D);
+    f.k = packed_view(p->k, r0, Hk, D);
+    f.v = packed_view(p->v, r0, Hk, D);
+    f.o = static_cast<uint16_t*>(p->o) + r0 * p->H * D;
+    f.o_stride[0] = (int64_t)len * p->H * D, f.o_stride[1] = D, f.o_stride[2] = (int64_t)p->H * D;
+    f.lse = p->lse ? p->lse + r0 : nullptr;
+    f.lse_stride[0] = total * p->H, f.lse_stride[1] = total;
+    f.B = 1, f.H = p->H, f.T = len, f.D = D, f.H_kv = Hk;
+    f.dtype = p->dtype, f.context_size = p->context_size, f.back_contexts = p->back_contexts;
+    f.sm_scale = p->sm_scale, f.flags = p->flags, f.status = p->status;
+    rc = kb_sa_fwd(&f, stream);
+    if (rc) return rc;
+  }
+  return KB_OK;
+}
+
+int kb_sa_bwd_varlen(const kb_sa_varlen_params* p, void* stream) {
+  int rc = check_varlen(p, true);
+  if (rc || p->B == 0) return rc;
+  const int32_t Hk = p->H_kv > 0 ? p->H_kv : p->H, D = p->D;
+  const int64_t total = p->cu_seqlens[p->B];
+  for (int32_t b = 0; b < p->B; ++b) {
+    const int64_t r0 = p->cu_seqlens[b];
+    const int32_t len = p->cu_seqlens[b + 1] - p->cu_seqlens[b];
+    if (len == 0) continue;
+    kb_sa_bwd_params g = {};
+    g.q = packed_view(p->q, r0, p->H, D);
+    g.k = packed_view(p->k, r0, Hk, D);
+    g.v = packed_view(p->v, r0, Hk, D);
+    g.o = packed_view(p->o, r0, p->H, D);
+    g.d_o = packed_view(p->d_o, r0, p->H, D);
+    g.lse = p->lse + r0;
+    g.lse_stride[0] = total * p->H, g.lse_stride[1] = total;
+    g.dq = static_cast<uint16_t*>(p->dq) + r0 * p->H * D;
+    g.dq_stride[0] = (int64_t)len * p->H * D, g.dq_stride[1] = D, g.dq_stride[2] = (int64_t)p->H * D;
+    g.dk = static_cast<uint16_t*>(p->dk) + r0 * Hk * D;
+    g.dv = static_cast<uint16_t*>(p->dv) + r0 * Hk * D;
+    g.dkv_stride[0] = (int64_t)len * Hk * D, g.dkv_stride[1] = D, g.dkv_stride[2] = (int64_t)Hk * D;
+    g.delta_ws = p->delta_ws, g.ds_ws = p->ds_ws, g.ds_ws_bytes = p->ds_ws_bytes;
+    g.B = 1, g.H = p->H, g.T = len, g.D = D, g.H_kv = Hk;
+    g.dtype = p->dtype, g.context_size = p->context_size, g.back_contexts = p->back_contexts;
+    g.sm_scale = p->sm_scale, g.flags = p->flags & ~KB_FLAG_BWD_TWO_PASS, g.status = p->status;
+    rc = kb_sa_bwd(&g, stream);
+    if (rc) return rc;
+  }
+  return KB_OK;
 }
 
 uint64_t kb_sa_bwd_workspace_bytes(int32_t B, int32_t H, int32_t T, int32_t D, int32_t dtype, int32_t context_size,

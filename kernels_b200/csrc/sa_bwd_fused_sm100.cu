@@ -88,6 +88,8 @@ struct FusedArgs {
   void* dq;
   const int32_t* lens;
   int64_t lens_stride;
+  int64_t lse_sb, lse_sh;                      // element strides of lse (b, h)
+  int64_t dq_sb, dq_sh, dq_st, dkv_sb, dkv_sh, dkv_st;  // of dq and of dk / dv (b, h, t)
   int32_t B, H, T, c, back, W;
   int32_t Hk, group;  // key/value heads and query heads per key/value head (H = Hk * group)
   KbFastDiv fd_tiles, fd_H, fd_Hk, fd_group, fd_c;  // division by ceil(T / 128), H, Hk, group and c
@@ -325,18 +327,20 @@ sa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
           }
           KB_FTR(0, g, 2);
         }
-        // lse and delta of the tile's query rows, two slots deep: slot g & 1 was last read while
-        // dS(g - 2) was formed
+        // lse and delta of the tile's query rows, two slots deep: slot g & 1 was last read while dS(g - 2) was
+        // formed.  The P phase of tile g needs them the moment S(g) completes and this warp gets here only
+        // after the wait for the dO buffer, so the loop is kept short: two 64-bit multiplies per element in it
+        // cost the kernel 15 % (staging first in the loop body, or before the dO load, changed nothing).
         if (ok && g >= 2) ok = mbar_wait<kRelaxedNs>(&sm.ds_ready[g & 1], ((g >> 1) - 1) & 1, ctx, kWStatsSlot);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
-        const int64_t bh = (int64_t)c.it.b * a.H + hq;
+        const float* lse_row = a.lse + (c.it.b * a.lse_sb + hq * a.lse_sh) + q0 + lane;
+        const float* delta_row = a.delta + ((int64_t)c.it.b * a.H + hq) * T + q0 + lane;
 #pragma unroll
         for (int i = 0; i < kBQ / 32; ++i) {
-          const int r = q0 + lane + 32 * i;
-          const bool valid = r < c.it.len;
-          sm.lse_s[g & 1][lane + 32 * i] = valid ? a.lse[bh * T + r] : 0.f;
-          sm.delta_s[g & 1][lane + 32 * i] = valid ? a.delta[bh * T + r] : 0.f;
+          const bool valid = q0 + lane + 32 * i < c.it.len;
+          sm.lse_s[g & 1][lane + 32 * i] = valid ? lse_row[32 * i] : 0.f;
+          sm.delta_s[g & 1][lane + 32 * i] = valid ? delta_row[32 * i] : 0.f;
         }
         mbar_arrive(&sm.stats_full[g & 1]);
       }
@@ -608,13 +612,13 @@ sa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
     it.b = -1;
     for (int item = blockIdx.x; ok && item < n_items; item += gridDim.x) {
       it = decode_item(a, item, n_ktiles, it);
-      const int64_t bh = (int64_t)it.b * a.Hk + it.hk;  // dV and dK have one head per key/value head
       const int kr = it.k0 + row;
       if (it.qr.begin >= it.qr.end) {
         // the whole key tile lies in the padding: its gradients are zeros (rare; plain stores)
         if (kr < T) {
-          uint4* dv_row = reinterpret_cast<uint4*>(static_cast<uint16_t*>(a.dv) + (bh * T + kr) * D);
-          uint4* dk_row = reinterpret_cast<uint4*>(static_cast<uint16_t*>(a.dk) + (bh * T + kr) * D);
+          const int64_t off = it.b * a.dkv_sb + it.hk * a.dkv_sh + kr * a.dkv_st;  // one head per key/value head
+          uint4* dv_row = reinterpret_cast<uint4*>(static_cast<uint16_t*>(a.dv) + off);
+          uint4* dk_row = reinterpret_cast<uint4*>(static_cast<uint16_t*>(a.dk) + off);
 #pragma unroll
           for (int i = 0; i < D * 2 / 16; ++i) {
             dv_row[i] = make_uint4(0, 0, 0, 0);
@@ -886,7 +890,7 @@ sa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
       if (it.kr.begin >= it.kr.end) {
         // the whole query tile lies in the padding: its gradient is zero (rare; plain stores)
         if (qi < T) {
-          uint4* dq_row = reinterpret_cast<uint4*>(static_cast<uint16_t*>(a.dq) + (((int64_t)it.b * a.H + it.h) * T + qi) * D);
+          uint4* dq_row = reinterpret_cast<uint4*>(static_cast<uint16_t*>(a.dq) + it.b * a.dq_sb + it.h * a.dq_sh + qi * a.dq_st);
 #pragma unroll
           for (int i = 0; i < D * 2 / 16; ++i) dq_row[i] = make_uint4(0, 0, 0, 0);
         }
@@ -945,9 +949,9 @@ int launch_fused(const kb_sa_bwd_params& p, int32_t c, int32_t back, cudaStream_
   const int32_t Hk = p.H_kv > 0 ? p.H_kv : p.H;
   if (!make_tile_map_4d(&tm_k, p.k, p.B, Hk, p.T, D, kBK) || !make_tile_map_4d(&tm_v, p.v, p.B, Hk, p.T, D, kBK) ||
       !make_tile_map_4d(&tm_q, p.q, p.B, p.H, p.T, D, kBQ) || !make_tile_map_4d(&tm_do, p.d_o, p.B, p.H, p.T, D, kBQ) ||
-      !make_tile_map_4d_contiguous(&tm_dk, p.dk, p.B, Hk, p.T, D, kBK) ||
-      !make_tile_map_4d_contiguous(&tm_dv, p.dv, p.B, Hk, p.T, D, kBK) ||
-      !make_tile_map_4d_contiguous(&tm_dq, p.dq, p.B, p.H, p.T, D, kBQ))
+      !make_tile_map_4d(&tm_dk, out_view(p.dk, p.dkv_stride, Hk, p.T, D), p.B, Hk, p.T, D, kBK) ||
+      !make_tile_map_4d(&tm_dv, out_view(p.dv, p.dkv_stride, Hk, p.T, D), p.B, Hk, p.T, D, kBK) ||
+      !make_tile_map_4d(&tm_dq, out_view(p.dq, p.dq_stride, p.H, p.T, D), p.B, p.H, p.T, D, kBQ))
     return KB_ERR_UNSUPPORTED;
   const int n_tiles = kb_cdiv_i32(p.T, kBQ);
   const int64_t n_items = (int64_t)p.B * p.H * n_tiles;
@@ -986,6 +990,14 @@ int launch_fused(const kb_sa_bwd_params& p, int32_t c, int32_t back, cudaStream_
 
   FusedArgs fa;
   fa.lse = p.lse;
+  {
+    const kb_tensor4 qv = out_view(p.dq, p.dq_stride, p.H, p.T, D), kv = out_view(p.dk, p.dkv_stride, Hk, p.T, D);
+    fa.dq_sb = qv.stride[0], fa.dq_sh = qv.stride[1], fa.dq_st = qv.stride[2];
+    fa.dkv_sb = kv.stride[0], fa.dkv_sh = kv.stride[1], fa.dkv_st = kv.stride[2];
+    const bool lse_packed = p.lse_stride[0] == 0 && p.lse_stride[1] == 0;
+    fa.lse_sb = lse_packed ? (int64_t)p.H * p.T : p.lse_stride[0];
+    fa.lse_sh = lse_packed ? (int64_t)p.T : p.lse_stride[1];
+  }
   fa.delta = p.delta_ws;
   fa.ds_ws = static_cast<uint8_t*>(p.ds_ws);
   fa.dk = p.dk;

@@ -67,6 +67,7 @@ struct FwdArgs {
   float* lse;
   const int32_t* lens;
   int64_t lens_stride;
+  int64_t o_sb, o_sh, o_st, lse_sb, lse_sh;  // element strides of o (b, h, t) and of lse (b, h)
   int32_t B, H, T, c, back;
   KbFastDiv fd_qblocks, fd_H, fd_c, fd_group;  // division by ceil(T / 256), H, c and H / H_kv (query heads per K/V head)
   float scale_log2;
@@ -373,9 +374,8 @@ sa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     for (int item = blockIdx.x; ok && item < n_items; item += gridDim.x) {
       const Item it = decode(item);
       const int qi = it.q0 + x * kBM + row;
-      const int64_t bh = (int64_t)it.b * a.H + it.h;
-      uint16_t* o_row = static_cast<uint16_t*>(a.o) + (bh * T + qi) * D;
-      float* lse_row = a.lse ? a.lse + bh * T + qi : nullptr;
+      uint16_t* o_row = static_cast<uint16_t*>(a.o) + it.b * a.o_sb + it.h * a.o_sh + qi * a.o_st;
+      float* lse_row = a.lse ? a.lse + it.b * a.lse_sb + it.h * a.lse_sh + qi : nullptr;
       if (!it.act[x]) {
         // this q tile lies wholly in the padding: its rows are zeros
         if (qi < T) {
@@ -495,7 +495,7 @@ int launch(const kb_sa_fwd_params& p, int32_t c, int32_t back, cudaStream_t s) {
   CUtensorMap tm_q, tm_k, tm_v, tm_o;
   const int32_t H_kv = p.H_kv > 0 ? p.H_kv : p.H;
   if (!make_tile_map_4d(&tm_q, p.q, p.B, p.H, p.T, D, kBM) || !make_tile_map_4d(&tm_k, p.k, p.B, H_kv, p.T, D, kBN) ||
-      !make_tile_map_4d(&tm_v, p.v, p.B, H_kv, p.T, D, kBN) || !make_tile_map_4d_contiguous(&tm_o, p.o, p.B, p.H, p.T, D, kBM))
+      !make_tile_map_4d(&tm_v, p.v, p.B, H_kv, p.T, D, kBN) || !make_tile_map_4d(&tm_o, out_view(p.o, p.o_stride, p.H, p.T, D), p.B, p.H, p.T, D, kBM))
     return KB_ERR_UNSUPPORTED;
   auto kern = sa_fwd_sm100_kernel<D, BF16>;
   constexpr size_t smem = sizeof(FwdSmem<D>);
@@ -506,6 +506,13 @@ int launch(const kb_sa_fwd_params& p, int32_t c, int32_t back, cudaStream_t s) {
   a.lse = p.lse;
   a.lens = p.lens;
   a.lens_stride = p.lens_stride;
+  {
+    const kb_tensor4 ov = out_view(p.o, p.o_stride, p.H, p.T, D);
+    a.o_sb = ov.stride[0], a.o_sh = ov.stride[1], a.o_st = ov.stride[2];
+    const bool lse_packed = p.lse_stride[0] == 0 && p.lse_stride[1] == 0;
+    a.lse_sb = lse_packed ? (int64_t)p.H * p.T : p.lse_stride[0];
+    a.lse_sh = lse_packed ? (int64_t)p.T : p.lse_stride[1];
+  }
   a.B = p.B;
   a.H = p.H;
   a.T = p.T;

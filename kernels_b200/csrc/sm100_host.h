@@ -52,6 +52,19 @@ inline bool make_tile_map_4d(CUtensorMap* out, const kb_tensor4& t, int B, int H
   return r == CUDA_SUCCESS;
 }
 
+// An output tensor as a strided view: `stride` holds the element strides of its b, h, t axes, all zeros
+// meaning [B, H, T, D] contiguous.
+inline kb_tensor4 out_view(void* data, const int64_t (&stride)[3], int H, int T, int D) {
+  kb_tensor4 t;
+  t.data = data;
+  const bool packed = stride[0] == 0 && stride[1] == 0 && stride[2] == 0;
+  t.stride[0] = packed ? (int64_t)H * T * D : stride[0];
+  t.stride[1] = packed ? (int64_t)T * D : stride[1];
+  t.stride[2] = packed ? (int64_t)D : stride[2];
+  t.stride[3] = 1;
+  return t;
+}
+
 // Map over a contiguous 16-bit [B, H, T, D] output tensor (same boxes as the inputs).
 inline bool make_tile_map_4d_contiguous(CUtensorMap* out, void* data, int B, int H, int T, int D, int box_rows) {
   kb_tensor4 t;

@@ -1,1 +1,2 @@
 from .kernel import streaming_attention, streaming_attention_reference  # noqa: F401
+from .varlen import streaming_attention_varlen  # noqa: F401

@@ -183,3 +183,50 @@ def test_backward_workspace_size():
     # no single-evaluation kernel for fp32 or other head dims: no scratch wanted
     assert lib.kb_sa_bwd_workspace_bytes(2, 3, 700, 64, _lib.KB_F32, 48, 3) == 0
     assert lib.kb_sa_bwd_workspace_bytes(2, 3, 700, 32, _lib.KB_F16, 48, 3) == 0
+
+
+def test_packed_batch_argument_validation_without_a_gpu():
+    lib = _lib.load()
+    assert lib.kb_sa_fwd_varlen(None, None) == 1 and lib.kb_sa_bwd_varlen(None, None) == 1
+    p = _lib.SaVarlenParams()
+    p.B, p.H, p.D, p.dtype, p.context_size, p.back_contexts = 0, 2, 64, _lib.KB_F16, 4, 1
+    assert lib.kb_sa_fwd_varlen(ctypes.byref(p), None) == 0          # empty batch: nothing to do
+    p.B = 2
+    assert lib.kb_sa_fwd_varlen(ctypes.byref(p), None) == 1          # no cu_seqlens
+    cu = (ctypes.c_int32 * 3)(0, 5, 3)
+    p.cu_seqlens = ctypes.cast(cu, ctypes.c_void_p)
+    assert lib.kb_sa_fwd_varlen(ctypes.byref(p), None) == 1          # decreasing
+    cu[2] = 5
+    cu[1] = 0
+    cu2 = (ctypes.c_int32 * 3)(0, 0, 0)
+    p.cu_seqlens = ctypes.cast(cu2, ctypes.c_void_p)
+    assert lib.kb_sa_fwd_varlen(ctypes.byref(p), None) == 0          # only empty sequences
+    p.cu_seqlens = ctypes.cast(cu, ctypes.c_void_p)
+    assert lib.kb_sa_fwd_varlen(ctypes.byref(p), None) == 1          # null tensors
+    p.H_kv = 3
+    assert lib.kb_sa_fwd_varlen(ctypes.byref(p), None) == 1          # 3 key/value heads do not divide 2
+    p.H_kv, p.D = 0, 32
+    assert lib.kb_sa_fwd_varlen(ctypes.byref(p), None) == 2          # tcgen05 kernels only: head_dim 64 / 128
+    p.D, p.dtype = 64, _lib.KB_F32
+    assert lib.kb_sa_bwd_varlen(ctypes.byref(p), None) == 2
+    p.dtype, p.context_size = _lib.KB_BF16, 0
+    assert lib.kb_sa_bwd_varlen(ctypes.byref(p), None) == 1
+
+
+def test_strided_outputs_are_validated_without_a_gpu():
+    lib = _lib.load()
+    buf = (ctypes.c_uint16 * 4096)()
+    ptr = ctypes.cast(buf, ctypes.c_void_p)
+    p = _lib.SaFwdParams()
+    p.B, p.H, p.T, p.D, p.dtype, p.context_size, p.back_contexts = 1, 1, 8, 64, _lib.KB_F16, 4, 1
+    for t in (p.q, p.k, p.v):
+        t.data = ptr
+        t.stride[0], t.stride[1], t.stride[2], t.stride[3] = 512, 512, 64, 1
+    p.o = ptr
+    p.sm_scale = 0.125
+    p.o_stride[0], p.o_stride[1], p.o_stride[2] = 512, 64, 67
+    assert lib.kb_sa_fwd(ctypes.byref(p), None) == 1                 # rows must stay 16-byte aligned
+    p.o_stride[2] = 0
+    assert lib.kb_sa_fwd(ctypes.byref(p), None) == 1                 # a strided output needs a row stride
+    p.o_stride[2] = -64
+    assert lib.kb_sa_fwd(ctypes.byref(p), None) == 1
