@@ -407,6 +407,34 @@ def run_own(args, w):
     if world > 1:
         dist.all_reduce(te, op=dist.ReduceOp.MAX)
     e2e_ms = float(te.item()) / max(e2e_steps, 1)
+    # the link the end-to-end leg is bound by: plain pinned copies of one chunk's tensors, each direction
+    # alone and both at once (outside the timed region; boxes of one pool differ in what they reach)
+    pcie = None
+    if e2e_steps:
+        def copy_rate(h2d, d2h):
+            c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize(dev)
+            c0.record(stream)
+            s_in.wait_stream(stream)
+            s_out.wait_stream(stream)
+            with torch.no_grad():
+                if h2d:
+                    with torch.cuda.stream(s_in):
+                        for dst, src in zip(dev_in[0], host_in[0]):
+                            dst.copy_(src, non_blocking=True)
+                if d2h:
+                    with torch.cuda.stream(s_out):
+                        for dst, src in zip(host_out[0], dev_in[-1]):
+                            dst.copy_(src, non_blocking=True)
+            stream.wait_stream(s_in)
+            stream.wait_stream(s_out)
+            c1.record(stream)
+            torch.cuda.synchronize(dev)
+            one_way = 4 * dev_in[0][0].numel() * dev_in[0][0].element_size()
+            return one_way / (c0.elapsed_time(c1) * 1e-3) / 1e9
+        copy_rate(True, True)
+        pcie = {"h2d_gbs": copy_rate(True, False), "d2h_gbs": copy_rate(False, True),
+                "both_gbs_per_direction": copy_rate(True, True)}
     tensor_bytes = q.numel() * q.element_size()
     _lib.check_device_status()
 
@@ -446,7 +474,7 @@ def run_own(args, w):
                          / peaks["hbm_gbs"]},
             "e2e": None if not e2e_steps else {"value": flops_total / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": 4 * tensor_bytes * world, "d2h_bytes_per_step": 4 * tensor_bytes * world,
-                    "steps": e2e_steps},
+                    "steps": e2e_steps, "pcie_copy_rates": pcie},
             "gpu_launches": launches,
             "clocks": clk.summary(),
         }
@@ -512,12 +540,58 @@ def run_dense(args):
     print(json.dumps(line))
 
 
+def run_step(args):
+    """The streaming inference step (no counterpart in the reference's benchmarks): 64 streams x 32 heads,
+    bf16 D=128 c=256 back=2, the 256 queries of the newest chunk against a cache of back + 1 = 3 chunks.
+    K + V of the cache are 805 MB and q + o 268 MB: more than L2, no flush.  Useful FLOPs 4*D*pairs with
+    pairs = c * 3c per (stream, head); algorithmic bytes: q, k, v read and o written once."""
+    from kernels_b200 import _lib
+    from kernels_b200.streaming_attention import streaming_attention_step
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    peaks = _peaks()
+    B, H, D, c, back = 64, 32, 128, 256, 2
+    T = (back + 1) * c
+    g = torch.Generator(device=dev).manual_seed(0)
+    q = torch.randn(B, H, c, D, device=dev, generator=g).bfloat16()
+    k, v = (torch.randn(B, H, T, D, device=dev, generator=g).bfloat16() for _ in range(2))
+    launches0 = _lib.launch_count()
+    for _ in range(max(args.warmup, 3)):
+        streaming_attention_step(q, k, v, None, c, back)
+    torch.cuda.synchronize()
+    with ClockSampler(0) as clk:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            streaming_attention_step(q, k, v, None, c, back)
+        e1.record()
+        torch.cuda.synchronize()
+    _lib.check_device_status()
+    ms = e0.elapsed_time(e1) / args.steps
+    flops = 4.0 * D * B * H * c * T
+    nbytes = 2.0 * (2 * q.numel() + 2 * k.numel())
+    line = {
+        "metric": "streaming step useful TFLOP/s", "value": flops / ms / 1e9, "unit": "TFLOP/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "kernels_b200",
+        "config": {"workload": "bf16 64 streams H=32 D=128 context=256 back=2: newest chunk against a 3-chunk cache",
+                   "name": "step", "l2": "inputs larger than L2 (no flush needed)"},
+        "roofline": {"kernel": "sa_fwd_sm100_kernel (q_start = 512)", "bound": "hbm", "achieved": nbytes / ms / 1e6,
+                     "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": nbytes / ms / 1e6 / peaks["hbm_gbs"],
+                     "peak_source": peaks["source"], "traffic": None, "algorithmic_bytes_per_launch": nbytes},
+        "tensor_frac_of_measured": flops / ms / 1e9 / peaks["tflops"],
+        "gpu_launches": _lib.launch_count() - launches0, "clocks": clk.summary(),
+    }
+    print(json.dumps(line))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--workload", default="cfg3", choices=sorted(WORKLOADS) + ["cfg4"])
+    ap.add_argument("--workload", default="cfg3", choices=sorted(WORKLOADS) + ["cfg4", "step"])
     ap.add_argument("--impl", default="own", choices=["own", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
@@ -526,6 +600,8 @@ def main():
     args = ap.parse_args()
     if args.workload == "cfg4":
         return run_dense(args)
+    if args.workload == "step":
+        return run_step(args)
     w = WORKLOADS[args.workload]
     if args.impl == "reference":
         run_reference(args, w)

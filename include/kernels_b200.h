@@ -103,6 +103,13 @@ typedef struct kb_sa_fwd_params {
    * tcgen05 kernels take a strided output; other calls return KB_ERR_UNSUPPORTED with nothing launched. */
   int64_t o_stride[3];
   int64_t lse_stride[2];
+  /* Streaming step (an extension; the reference has no key/value cache, its mask, kernel.py:1540-1542,
+   * defines the result): 0 for the reference's call.  Otherwise only the queries of the positions
+   * [q_start, T) are given and computed: q, o and lse have T - q_start rows, row r standing at position
+   * q_start + r, while k and v hold all T positions (an inference step: the new chunk of queries against a
+   * cache of the last back_contexts + 1 chunks, whose first row must lie on a chunk boundary).  `lens` still
+   * counts positions.  Only the tcgen05 kernels take q_start != 0; other calls return KB_ERR_UNSUPPORTED. */
+  int32_t q_start;
 } kb_sa_fwd_params;
 
 KB_API int kb_sa_fwd(const kb_sa_fwd_params* p, void* stream);

@@ -44,6 +44,7 @@ class SaFwdParams(C.Structure):
         ("sm_scale", C.c_float), ("flags", C.c_uint32), ("status", C.c_void_p),
         ("H_kv", C.c_int32),
         ("o_stride", C.c_int64 * 3), ("lse_stride", C.c_int64 * 2),
+        ("q_start", C.c_int32),
     ]
 
 

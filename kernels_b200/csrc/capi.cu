@@ -97,6 +97,7 @@ int run_fwd(const kb_sa_fwd_params* p, void* stream, bool dense) {
   if (empty(p->B, p->H, p->T)) return KB_OK;
   if (!p->q.data || !p->k.data || !p->v.data || !p->o) return KB_ERR_BAD_ARGUMENT;
   if (!out_stride_ok(p->o_stride) || p->lse_stride[0] < 0 || p->lse_stride[1] < 0) return KB_ERR_BAD_ARGUMENT;
+  if (p->q_start < 0 || p->q_start >= p->T) return KB_ERR_BAD_ARGUMENT;
   const bool strided_out = any_stride(p->o_stride) || any_stride(p->lse_stride);
   const int32_t c = dense ? kb_max_i32(p->T, 1) : kb_clamp_context(p->context_size, p->T);
   const int32_t back = dense ? 0 : kb_clamp_back(p->back_contexts, p->T, c);
@@ -109,8 +110,8 @@ int run_fwd(const kb_sa_fwd_params* p, void* stream, bool dense) {
     if (rc != KB_ERR_UNSUPPORTED) return rc;
   }
 #endif
-  // the generic kernels want one K/V head per query head and contiguous outputs
-  if (kv_heads(p) != p->H || strided_out) return KB_ERR_UNSUPPORTED;
+  // the generic kernels want one K/V head per query head, contiguous outputs and every query row
+  if (kv_heads(p) != p->H || strided_out || p->q_start) return KB_ERR_UNSUPPORTED;
   return sa_fwd_generic(*p, c, back, s);
 }
 

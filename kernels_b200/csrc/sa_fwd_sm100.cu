@@ -69,6 +69,7 @@ struct FwdArgs {
   int64_t lens_stride;
   int64_t o_sb, o_sh, o_st, lse_sb, lse_sh;  // element strides of o (b, h, t) and of lse (b, h)
   int32_t B, H, T, c, back;
+  int32_t q_start;  // the query rows are the positions [q_start, T): row r of q / o / lse is position q_start + r
   KbFastDiv fd_qblocks, fd_H, fd_c, fd_group;  // division by ceil(T / 256), H, c and H / H_kv (query heads per K/V head)
   float scale_log2;
   int32_t* status;
@@ -167,7 +168,7 @@ sa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int T = a.T;
-  const int n_qblocks = kb_cdiv_i32(T, kBM * kQTiles);
+  const int n_qblocks = kb_cdiv_i32(T - a.q_start, kBM * kQTiles);
   const int n_items = a.B * a.H * n_qblocks;
 
   if (smem_u32(smem_raw) & 1023u) {
@@ -193,7 +194,7 @@ sa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     const int bh = kb_fastdiv(item, a.fd_qblocks), qb = item - bh * n_qblocks;
     it.b = kb_fastdiv(bh, a.fd_H);
     it.h = bh - it.b * a.H;
-    it.q0 = qb * (kBM * kQTiles);
+    it.q0 = a.q_start + qb * (kBM * kQTiles);
     it.len = a.lens ? kb_clamp_len(a.lens[(int64_t)it.b * a.lens_stride], T) : T;
 #pragma unroll
     for (int x = 0; x < kQTiles; ++x) {
@@ -256,7 +257,7 @@ sa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
           if (!it.act[x]) continue;
 #pragma unroll
           for (int p = 0; p < kPanels; ++p)
-            tma_load_4d(sm.q[x] + p * kPanelBytes, &tm_q, &sm.q_full, p * 64, it.q0 + x * kBM, it.h, it.b);
+            tma_load_4d(sm.q[x] + p * kPanelBytes, &tm_q, &sm.q_full, p * 64, it.q0 - a.q_start + x * kBM, it.h, it.b);
         }
         const int h_kv = kb_fastdiv(it.h, a.fd_group);  // the K/V head this query head reads
         for (int t = it.u_begin; t < it.u_end; ++t, ++kc, ++vc) {
@@ -374,8 +375,8 @@ sa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     for (int item = blockIdx.x; ok && item < n_items; item += gridDim.x) {
       const Item it = decode(item);
       const int qi = it.q0 + x * kBM + row;
-      uint16_t* o_row = static_cast<uint16_t*>(a.o) + it.b * a.o_sb + it.h * a.o_sh + qi * a.o_st;
-      float* lse_row = a.lse ? a.lse + it.b * a.lse_sb + it.h * a.lse_sh + qi : nullptr;
+      uint16_t* o_row = static_cast<uint16_t*>(a.o) + it.b * a.o_sb + it.h * a.o_sh + (qi - a.q_start) * a.o_st;
+      float* lse_row = a.lse ? a.lse + it.b * a.lse_sb + it.h * a.lse_sh + (qi - a.q_start) : nullptr;
       if (!it.act[x]) {
         // this q tile lies wholly in the padding: its rows are zeros
         if (qi < T) {
@@ -468,7 +469,7 @@ sa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         fence_proxy_async();  // the store reads shared memory through the async proxy
         named_barrier_sync(1 + x, kBM);
         if (row == 0) {
-          tma_store_4d(&tm_o, sm.o_stage[x], p * 64, it.q0 + x * kBM, it.h, it.b);
+          tma_store_4d(&tm_o, sm.o_stage[x], p * 64, it.q0 - a.q_start + x * kBM, it.h, it.b);
           tma_store_commit();
         }
       }
@@ -494,8 +495,9 @@ template <int D, bool BF16>
 int launch(const kb_sa_fwd_params& p, int32_t c, int32_t back, cudaStream_t s) {
   CUtensorMap tm_q, tm_k, tm_v, tm_o;
   const int32_t H_kv = p.H_kv > 0 ? p.H_kv : p.H;
-  if (!make_tile_map_4d(&tm_q, p.q, p.B, p.H, p.T, D, kBM) || !make_tile_map_4d(&tm_k, p.k, p.B, H_kv, p.T, D, kBN) ||
-      !make_tile_map_4d(&tm_v, p.v, p.B, H_kv, p.T, D, kBN) || !make_tile_map_4d(&tm_o, out_view(p.o, p.o_stride, p.H, p.T, D), p.B, p.H, p.T, D, kBM))
+  const int32_t Tq = p.T - p.q_start;  // rows of q, o and lse
+  if (!make_tile_map_4d(&tm_q, p.q, p.B, p.H, Tq, D, kBM) || !make_tile_map_4d(&tm_k, p.k, p.B, H_kv, p.T, D, kBN) ||
+      !make_tile_map_4d(&tm_v, p.v, p.B, H_kv, p.T, D, kBN) || !make_tile_map_4d(&tm_o, out_view(p.o, p.o_stride, p.H, Tq, D), p.B, p.H, Tq, D, kBM))
     return KB_ERR_UNSUPPORTED;
   auto kern = sa_fwd_sm100_kernel<D, BF16>;
   constexpr size_t smem = sizeof(FwdSmem<D>);
@@ -507,24 +509,25 @@ int launch(const kb_sa_fwd_params& p, int32_t c, int32_t back, cudaStream_t s) {
   a.lens = p.lens;
   a.lens_stride = p.lens_stride;
   {
-    const kb_tensor4 ov = out_view(p.o, p.o_stride, p.H, p.T, D);
+    const kb_tensor4 ov = out_view(p.o, p.o_stride, p.H, Tq, D);
     a.o_sb = ov.stride[0], a.o_sh = ov.stride[1], a.o_st = ov.stride[2];
     const bool lse_packed = p.lse_stride[0] == 0 && p.lse_stride[1] == 0;
-    a.lse_sb = lse_packed ? (int64_t)p.H * p.T : p.lse_stride[0];
-    a.lse_sh = lse_packed ? (int64_t)p.T : p.lse_stride[1];
+    a.lse_sb = lse_packed ? (int64_t)p.H * Tq : p.lse_stride[0];
+    a.lse_sh = lse_packed ? (int64_t)Tq : p.lse_stride[1];
   }
   a.B = p.B;
   a.H = p.H;
   a.T = p.T;
   a.c = c;
   a.back = back;
-  a.fd_qblocks = kb_fastdiv_make(kb_cdiv_i32(p.T, kBM * kQTiles));
+  a.q_start = p.q_start;
+  a.fd_qblocks = kb_fastdiv_make(kb_cdiv_i32(Tq, kBM * kQTiles));
   a.fd_H = kb_fastdiv_make(p.H);
   a.fd_c = kb_fastdiv_make(c);
   a.fd_group = kb_fastdiv_make(p.H / H_kv);
   a.scale_log2 = p.sm_scale * kLog2e;
   a.status = p.status;
-  const int64_t n_items = (int64_t)p.B * p.H * kb_cdiv_i32(p.T, kBM * kQTiles);
+  const int64_t n_items = (int64_t)p.B * p.H * kb_cdiv_i32(Tq, kBM * kQTiles);
   if (n_items > (int64_t)1 << 30) return KB_ERR_TOO_LARGE;
   int dev = 0, n_sm = 0;
   KB_CUDA_TRY(cudaGetDevice(&dev));

@@ -230,3 +230,22 @@ def test_strided_outputs_are_validated_without_a_gpu():
     assert lib.kb_sa_fwd(ctypes.byref(p), None) == 1                 # a strided output needs a row stride
     p.o_stride[2] = -64
     assert lib.kb_sa_fwd(ctypes.byref(p), None) == 1
+
+
+def test_streaming_step_start_is_validated_without_a_gpu():
+    lib = _lib.load()
+    buf = (ctypes.c_uint16 * 4096)()
+    ptr = ctypes.cast(buf, ctypes.c_void_p)
+    p = _lib.SaFwdParams()
+    p.B, p.H, p.T, p.D, p.dtype, p.context_size, p.back_contexts = 1, 1, 8, 64, _lib.KB_F16, 4, 1
+    for t in (p.q, p.k, p.v):
+        t.data = ptr
+        t.stride[0], t.stride[1], t.stride[2], t.stride[3] = 512, 512, 64, 1
+    p.o = ptr
+    p.sm_scale = 0.125
+    p.q_start = -1
+    assert lib.kb_sa_fwd(ctypes.byref(p), None) == 1                 # before the first position
+    p.q_start = 8
+    assert lib.kb_sa_fwd(ctypes.byref(p), None) == 1                 # no query row left
+    p.q_start, p.dtype = 4, _lib.KB_F32
+    assert lib.kb_sa_fwd(ctypes.byref(p), None) == 2                 # tcgen05 kernels only
