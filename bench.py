@@ -17,6 +17,9 @@ Prints ONE JSON line on rank 0:
                 timed on this machine's host cores on a bounded sample of the same workload.
 
 ``--impl reference`` times that CPU path alone (rank 0 only) and prints the same line shape.
+``--impl context`` (one GPU) times library kernels on the same inputs for context: compiled
+``flex_attention`` with the streaming block mask and torch SDPA with the dense mask.
+``--workload step`` times the streaming inference step, ``--workload cfg4`` dense self-attention and softmax.
 
 Multi-GPU: launched by ``torch.distributed.run`` with one rank per GPU.  The batch x heads
 slices are sharded over ranks (weak scaling for cfg3/cfg2: every rank gets a full copy of the
@@ -586,13 +589,83 @@ def run_step(args):
     print(json.dumps(line))
 
 
+def run_context(args, w):
+    """Context, not an arm of the comparison: library kernels on the SAME GPU and the SAME inputs as the
+    own arm (the reference's benchmark times these beside its kernel,
+    benchmark/benchmark_streaming_attention.py:173-243): ``flex_attention`` compiled with the streaming mask
+    as a block mask, and torch SDPA with the dense boolean mask where T x T fits.  Forward + backward,
+    useful TFLOP/s by the own arm's formula.  The reference's own Triton kernel cannot run on the
+    benchmark machine (its sources do not travel)."""
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    dtype = TORCH_DTYPES[w["dtype"]]
+    H, T, D, c, back = w["H"], w["T"], w["D"], w["c"], w["back"]
+    B, lens = _global_problem(w, 1)
+    hq, hk, hv, hdo = _make_local_inputs(w, B, list(range(H)), H, dtype, pin=False)
+    q, k, v, do = (t.to(dev) for t in (hq, hk, hv, hdo))
+    lens_d = torch.full((B,), T, dtype=torch.int32, device=dev) if lens is None else lens.to(dev)
+    pairs_total, _ = _useful_pairs_total(w, B, lens, H)
+    flops = 14.0 * D * pairs_total
+    scale = float(D ** -0.5)
+    steps, warm = max(1, min(args.steps, 10)), 3
+
+    def timed(fn):
+        for _ in range(warm):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / steps
+
+    def fwd_bwd(attn):
+        qg, kg, vg = (t.detach().requires_grad_() for t in (q, k, v))
+        attn(qg, kg, vg).backward(do)
+
+    out = {}
+    try:
+        from torch.nn.attention.flex_attention import create_block_mask, flex_attention
+
+        def mask_mod(b, h, qi, ki):
+            d = qi // c - ki // c
+            return (d >= 0) & (d <= back) & (qi < lens_d[b]) & (ki < lens_d[b])
+
+        bm = create_block_mask(mask_mod, B, None, T, T, device=dev, BLOCK_SIZE=128)
+        flex = torch.compile(flex_attention, dynamic=False)
+        ms = timed(lambda: fwd_bwd(lambda a, b_, c_: flex(a, b_, c_, block_mask=bm, scale=scale)))
+        out["flex_attention"] = {"ms_per_step": ms, "tflops": flops / ms / 1e9, "block_size": 128}
+    except Exception as e:  # context only: say why it is missing
+        out["flex_attention"] = {"unavailable": f"{type(e).__name__}: {str(e)[:200]}"}
+    torch.cuda.synchronize()
+    try:
+        if B * T * T > 6e9:
+            raise RuntimeError("dense mask too large")
+        pos = torch.arange(T, device=dev)
+        d = pos[:, None] // c - pos[None, :] // c
+        band = (d >= 0) & (d <= back)
+        valid = pos[None, :] < lens_d[:, None]
+        mask = (band[None] & valid[:, :, None] & valid[:, None, :])[:, None]
+        mask = mask | ~valid[:, None, :, None]  # padded rows see everything: no NaN (their dO is zero)
+        ms = timed(lambda: fwd_bwd(lambda a, b_, c_: torch.nn.functional.scaled_dot_product_attention(
+            a, b_, c_, attn_mask=mask, scale=scale)))
+        out["sdpa_dense_mask"] = {"ms_per_step": ms, "tflops": flops / ms / 1e9}
+    except Exception as e:
+        out["sdpa_dense_mask"] = {"unavailable": f"{type(e).__name__}: {str(e)[:200]}"}
+    print(json.dumps({"impl": "context", "metric": "streaming-attn fwd+bwd useful TFLOP/s", "unit": "TFLOP/s",
+                      "n_gpus": 1, "steps": steps, "warmup": warm, "dtype": w["dtype"], "data": "synthetic",
+                      "config": {"workload": w["desc"], "name": args.workload}, "library_kernels": out}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--workload", default="cfg3", choices=sorted(WORKLOADS) + ["cfg4", "step"])
-    ap.add_argument("--impl", default="own", choices=["own", "reference"])
+    ap.add_argument("--impl", default="own", choices=["own", "reference", "context"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     ap.add_argument("--two-pass", action="store_true",
@@ -603,6 +676,8 @@ def main():
     if args.workload == "step":
         return run_step(args)
     w = WORKLOADS[args.workload]
+    if args.impl == "context":
+        return run_context(args, w)
     if args.impl == "reference":
         run_reference(args, w)
     else:
