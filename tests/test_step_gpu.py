@@ -35,6 +35,7 @@ def _inputs(B, H, Hk, T, D, dtype, seed=5):
     (4, 1, 1024, 512, 64, 128, 3, torch.float16, None),          # shared K/V heads
     (2, 2, 1536, 768, 128, 48, 5, torch.bfloat16, [1536, 900]),  # lens inside the computed rows
     (2, 2, 700, 700, 64, 100, 1, torch.float16, [700, 1]),       # q_start = 0: the ordinary call
+    (2, 2, 1536, 768, 64, 128, 1, torch.float16, [1000, 100]),   # a batch element that ends before the first query
 ])
 def test_step_equals_full_call_bitwise_on_aligned_starts(H, Hk, T, Tq, D, c, back, dtype, lens):
     from kernels_b200.streaming_attention import streaming_attention, streaming_attention_step
