@@ -110,6 +110,13 @@ typedef struct kb_sa_fwd_params {
    * cache of the last back_contexts + 1 chunks, whose first row must lie on a chunk boundary).  `lens` still
    * counts positions.  Only the tcgen05 kernels take q_start != 0; other calls return KB_ERR_UNSUPPORTED. */
   int32_t q_start;
+  /* Packed batch in ONE launch (what kb_sa_fwd_varlen calls; NULL for every other call): DEVICE pointer to
+   * B + 1 non-decreasing row offsets.  q, k, v then describe one batch entry of `total_rows` rows (the batch
+   * stride is ignored), sequence b owning the rows [cu_seqlens[b], cu_seqlens[b + 1]); o_stride / lse_stride
+   * give the h and t strides of the packed outputs; T is the LONGEST sequence; lens must be NULL and q_start 0.
+   * tcgen05 kernels only. */
+  const int32_t* cu_seqlens;
+  int32_t total_rows;
 } kb_sa_fwd_params;
 
 KB_API int kb_sa_fwd(const kb_sa_fwd_params* p, void* stream);
@@ -218,6 +225,10 @@ typedef struct kb_sa_varlen_params {
   float sm_scale;
   uint32_t flags;
   int32_t* status;
+  /* The same offsets in DEVICE memory, or NULL.  When given, the forward is ONE launch over all sequences (the
+   * kernel reads a sequence's first row and length from it) instead of one launch per sequence (the host copy
+   * is still read, for the checks and the longest sequence).  The backward still launches per sequence. */
+  const int32_t* cu_seqlens_dev;
 } kb_sa_varlen_params;
 
 KB_API int kb_sa_fwd_varlen(const kb_sa_varlen_params* p, void* stream);

@@ -45,6 +45,7 @@ class SaFwdParams(C.Structure):
         ("H_kv", C.c_int32),
         ("o_stride", C.c_int64 * 3), ("lse_stride", C.c_int64 * 2),
         ("q_start", C.c_int32),
+        ("cu_seqlens", C.c_void_p), ("total_rows", C.c_int32),
     ]
 
 
@@ -73,6 +74,7 @@ class SaVarlenParams(C.Structure):
         ("B", C.c_int32), ("H", C.c_int32), ("H_kv", C.c_int32), ("D", C.c_int32),
         ("dtype", C.c_int32), ("context_size", C.c_int32), ("back_contexts", C.c_int32),
         ("sm_scale", C.c_float), ("flags", C.c_uint32), ("status", C.c_void_p),
+        ("cu_seqlens_dev", C.c_void_p),
     ]
 
 

@@ -98,6 +98,7 @@ int run_fwd(const kb_sa_fwd_params* p, void* stream, bool dense) {
   if (!p->q.data || !p->k.data || !p->v.data || !p->o) return KB_ERR_BAD_ARGUMENT;
   if (!out_stride_ok(p->o_stride) || p->lse_stride[0] < 0 || p->lse_stride[1] < 0) return KB_ERR_BAD_ARGUMENT;
   if (p->q_start < 0 || p->q_start >= p->T) return KB_ERR_BAD_ARGUMENT;
+  if (p->cu_seqlens && (dense || p->lens || p->q_start || p->total_rows < p->T)) return KB_ERR_BAD_ARGUMENT;
   const bool strided_out = any_stride(p->o_stride) || any_stride(p->lse_stride);
   const int32_t c = dense ? kb_max_i32(p->T, 1) : kb_clamp_context(p->context_size, p->T);
   const int32_t back = dense ? 0 : kb_clamp_back(p->back_contexts, p->T, c);
@@ -111,7 +112,7 @@ int run_fwd(const kb_sa_fwd_params* p, void* stream, bool dense) {
   }
 #endif
   // the generic kernels want one K/V head per query head, contiguous outputs and every query row
-  if (kv_heads(p) != p->H || strided_out || p->q_start) return KB_ERR_UNSUPPORTED;
+  if (kv_heads(p) != p->H || strided_out || p->q_start || p->cu_seqlens) return KB_ERR_UNSUPPORTED;
   return sa_fwd_generic(*p, c, back, s);
 }
 
@@ -190,6 +191,25 @@ int kb_sa_fwd_varlen(const kb_sa_varlen_params* p, void* stream) {
   if (rc || p->B == 0) return rc;
   const int32_t Hk = p->H_kv > 0 ? p->H_kv : p->H, D = p->D;
   const int64_t total = p->cu_seqlens[p->B];
+  if (total == 0) return KB_OK;
+  if (p->cu_seqlens_dev) {
+    // one launch: the kernel finds every sequence's first row and length in the device copy of the offsets
+    int32_t max_len = 0;
+    for (int32_t b = 0; b < p->B; ++b) max_len = kb_max_i32(max_len, p->cu_seqlens[b + 1] - p->cu_seqlens[b]);
+    kb_sa_fwd_params f = {};
+    f.q = packed_view(p->q, 0, p->H, D);
+    f.k = packed_view(p->k, 0, Hk, D);
+    f.v = packed_view(p->v, 0, Hk, D);
+    f.o = p->o;
+    f.o_stride[0] = total * p->H * D, f.o_stride[1] = D, f.o_stride[2] = (int64_t)p->H * D;
+    f.lse = p->lse;
+    f.lse_stride[0] = total * p->H, f.lse_stride[1] = total;
+    f.B = p->B, f.H = p->H, f.T = max_len, f.D = D, f.H_kv = Hk;
+    f.dtype = p->dtype, f.context_size = p->context_size, f.back_contexts = p->back_contexts;
+    f.sm_scale = p->sm_scale, f.flags = p->flags, f.status = p->status;
+    f.cu_seqlens = p->cu_seqlens_dev, f.total_rows = (int32_t)total;
+    return kb_sa_fwd(&f, stream);
+  }
   for (int32_t b = 0; b < p->B; ++b) {
     const int64_t r0 = p->cu_seqlens[b];
     const int32_t len = p->cu_seqlens[b + 1] - p->cu_seqlens[b];

@@ -70,6 +70,9 @@ struct FwdArgs {
   int64_t o_sb, o_sh, o_st, lse_sb, lse_sh;  // element strides of o (b, h, t) and of lse (b, h)
   int32_t B, H, T, c, back;
   int32_t q_start;  // the query rows are the positions [q_start, T): row r of q / o / lse is position q_start + r
+  // Packed batch: sequence b owns the rows [cu[b], cu[b + 1]) of tensors with ONE batch entry (the maps' batch
+  // extent is 1, o_sb = lse_sb = 0) and T is the longest sequence.  NULL: the padded layout.
+  const int32_t* cu;
   KbFastDiv fd_qblocks, fd_H, fd_c, fd_group;  // division by ceil(T / 256), H, c and H / H_kv (query heads per K/V head)
   float scale_log2;
   int32_t* status;
@@ -159,7 +162,7 @@ __device__ __forceinline__ float softmax_block(uint32_t t_s, float scale, int k0
   return alpha;
 }
 
-template <int D, bool BF16>
+template <int D, bool BF16, bool PACKED>  // PACKED: one launch over a packed batch (FwdArgs::cu)
 __global__ void __launch_bounds__(kThreads, 1)
 sa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                     const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o, const FwdArgs a) {
@@ -185,6 +188,7 @@ sa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   // earlier than A's, and they touch or overlap).  Every role decodes items the same way.
   struct Item {
     int b, h, q0, len;
+    int row0;  // first row of the sequence in the tensor maps (packed batch: cu[b], batch coordinate 0)
     KbTileRange kr[kQTiles];
     bool act[kQTiles];
     int u_begin, u_end;
@@ -196,6 +200,11 @@ sa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     it.h = bh - it.b * a.H;
     it.q0 = a.q_start + qb * (kBM * kQTiles);
     it.len = a.lens ? kb_clamp_len(a.lens[(int64_t)it.b * a.lens_stride], T) : T;
+    it.row0 = 0;
+    if (PACKED) {
+      it.row0 = a.cu[it.b];
+      it.len = kb_min_i32(a.cu[it.b + 1] - it.row0, T);
+    }
 #pragma unroll
     for (int x = 0; x < kQTiles; ++x) {
       it.kr[x] = kb_fwd_kv_range_fd(it.q0 + x * kBM, kBM, kBN, it.len, a.c, a.back, a.fd_c);
@@ -257,7 +266,7 @@ sa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
           if (!it.act[x]) continue;
 #pragma unroll
           for (int p = 0; p < kPanels; ++p)
-            tma_load_4d(sm.q[x] + p * kPanelBytes, &tm_q, &sm.q_full, p * 64, it.q0 - a.q_start + x * kBM, it.h, it.b);
+            tma_load_4d(sm.q[x] + p * kPanelBytes, &tm_q, &sm.q_full, p * 64, it.row0 + it.q0 - a.q_start + x * kBM, it.h, PACKED ? 0 : it.b);
         }
         const int h_kv = kb_fastdiv(it.h, a.fd_group);  // the K/V head this query head reads
         for (int t = it.u_begin; t < it.u_end; ++t, ++kc, ++vc) {
@@ -266,11 +275,11 @@ sa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
           if (kc >= kStagesK && !mbar_wait(&sm.k_empty[sk], ((kc / kStagesK) - 1) & 1, ctx, kWaitKEmpty)) { ok = false; break; }
           mbar_expect_tx(&sm.k_full[sk], kTileBytes);
 #pragma unroll
-          for (int p = 0; p < kPanels; ++p) tma_load_4d(sm.k[sk] + p * kPanelBytes, &tm_k, &sm.k_full[sk], p * 64, k0, h_kv, it.b);
+          for (int p = 0; p < kPanels; ++p) tma_load_4d(sm.k[sk] + p * kPanelBytes, &tm_k, &sm.k_full[sk], p * 64, it.row0 + k0, h_kv, PACKED ? 0 : it.b);
           if (vc >= kStagesV && !mbar_wait(&sm.v_empty[sv], ((vc / kStagesV) - 1) & 1, ctx, kWaitVEmpty)) { ok = false; break; }
           mbar_expect_tx(&sm.v_full[sv], kTileBytes);
 #pragma unroll
-          for (int p = 0; p < kPanels; ++p) tma_load_4d(sm.v[sv] + p * kPanelBytes, &tm_v, &sm.v_full[sv], p * 64, k0, h_kv, it.b);
+          for (int p = 0; p < kPanels; ++p) tma_load_4d(sm.v[sv] + p * kPanelBytes, &tm_v, &sm.v_full[sv], p * 64, it.row0 + k0, h_kv, PACKED ? 0 : it.b);
         }
         ++na;
       }
@@ -375,11 +384,12 @@ sa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     for (int item = blockIdx.x; ok && item < n_items; item += gridDim.x) {
       const Item it = decode(item);
       const int qi = it.q0 + x * kBM + row;
-      uint16_t* o_row = static_cast<uint16_t*>(a.o) + it.b * a.o_sb + it.h * a.o_sh + (qi - a.q_start) * a.o_st;
-      float* lse_row = a.lse ? a.lse + it.b * a.lse_sb + it.h * a.lse_sh + (qi - a.q_start) : nullptr;
+      const int orow = it.row0 + qi - a.q_start;  // this thread's row of o and lse
+      uint16_t* o_row = static_cast<uint16_t*>(a.o) + it.b * a.o_sb + it.h * a.o_sh + orow * a.o_st;
+      float* lse_row = a.lse ? a.lse + it.b * a.lse_sb + it.h * a.lse_sh + orow : nullptr;
       if (!it.act[x]) {
         // this q tile lies wholly in the padding: its rows are zeros
-        if (qi < T) {
+        if (qi < (PACKED ? it.len : T)) {  // a packed batch has no padding rows
           uint4* dst = reinterpret_cast<uint4*>(o_row);
 #pragma unroll
           for (int i = 0; i < D * 2 / 16; ++i) dst[i] = make_uint4(0, 0, 0, 0);
@@ -452,6 +462,23 @@ sa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       // lines per instruction and held the softmax warps for several thousand clocks per item.  Rows past
       // the end of the tensor are clipped by the store; rows past `len` are zeros (inv = 0).
       uint8_t* stage = sm.o_stage[x] + row * 128;
+      if (PACKED && it.q0 + x * kBM + kBM > it.len) {
+        // packed batch, last tile of a sequence: the rows below belong to the next sequence, so no box store;
+        // every thread writes its own row (one such tile per sequence and head)
+        if (valid) {
+          uint4* dst = reinterpret_cast<uint4*>(o_row);
+#pragma unroll
+          for (int j = 0; j < D / 8; ++j) {
+            const int e = 8 * j;
+            uint4 w;
+            w.x = pack16x2<BF16>(__uint_as_float(r[e + 0]) * inv, __uint_as_float(r[e + 1]) * inv);
+            w.y = pack16x2<BF16>(__uint_as_float(r[e + 2]) * inv, __uint_as_float(r[e + 3]) * inv);
+            w.z = pack16x2<BF16>(__uint_as_float(r[e + 4]) * inv, __uint_as_float(r[e + 5]) * inv);
+            w.w = pack16x2<BF16>(__uint_as_float(r[e + 6]) * inv, __uint_as_float(r[e + 7]) * inv);
+            dst[j] = w;
+          }
+        }
+      } else {
 #pragma unroll
       for (int p = 0; p < kPanels; ++p) {
         if (row == 0) tma_store_wait_read();  // the store that used the buffer last has read it
@@ -469,11 +496,12 @@ sa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         fence_proxy_async();  // the store reads shared memory through the async proxy
         named_barrier_sync(1 + x, kBM);
         if (row == 0) {
-          tma_store_4d(&tm_o, sm.o_stage[x], p * 64, it.q0 - a.q_start + x * kBM, it.h, it.b);
+          tma_store_4d(&tm_o, sm.o_stage[x], p * 64, it.row0 + it.q0 - a.q_start + x * kBM, it.h, PACKED ? 0 : it.b);
           tma_store_commit();
         }
       }
-      if (qi < T && lse_row) *lse_row = valid ? m_used + log2f(l) : 0.f;
+      }
+      if (qi < (PACKED ? it.len : T) && lse_row) *lse_row = valid ? m_used + log2f(l) : 0.f;
       KB_FACC(6);
     }
     if (row == 0) tma_store_wait_all();
@@ -491,15 +519,18 @@ sa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   }
 }
 
-template <int D, bool BF16>
+template <int D, bool BF16, bool PACKED>
 int launch(const kb_sa_fwd_params& p, int32_t c, int32_t back, cudaStream_t s) {
   CUtensorMap tm_q, tm_k, tm_v, tm_o;
   const int32_t H_kv = p.H_kv > 0 ? p.H_kv : p.H;
   const int32_t Tq = p.T - p.q_start;  // rows of q, o and lse
-  if (!make_tile_map_4d(&tm_q, p.q, p.B, p.H, Tq, D, kBM) || !make_tile_map_4d(&tm_k, p.k, p.B, H_kv, p.T, D, kBN) ||
-      !make_tile_map_4d(&tm_v, p.v, p.B, H_kv, p.T, D, kBN) || !make_tile_map_4d(&tm_o, out_view(p.o, p.o_stride, p.H, Tq, D), p.B, p.H, Tq, D, kBM))
+  // a packed batch is ONE batch entry of `total_rows` rows as far as the maps go
+  const int32_t mapB = p.cu_seqlens ? 1 : p.B, mapTq = p.cu_seqlens ? p.total_rows : Tq, mapT = p.cu_seqlens ? p.total_rows : p.T;
+  if (!make_tile_map_4d(&tm_q, p.q, mapB, p.H, mapTq, D, kBM) || !make_tile_map_4d(&tm_k, p.k, mapB, H_kv, mapT, D, kBN) ||
+      !make_tile_map_4d(&tm_v, p.v, mapB, H_kv, mapT, D, kBN) ||
+      !make_tile_map_4d(&tm_o, out_view(p.o, p.o_stride, p.H, mapTq, D), mapB, p.H, mapTq, D, kBM))
     return KB_ERR_UNSUPPORTED;
-  auto kern = sa_fwd_sm100_kernel<D, BF16>;
+  auto kern = sa_fwd_sm100_kernel<D, BF16, PACKED>;
   constexpr size_t smem = sizeof(FwdSmem<D>);
   static_assert(sizeof(FwdSmem<D>) <= 232448, "forward shared memory exceeds the 227 KB a CTA may have");
   KB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -509,11 +540,12 @@ int launch(const kb_sa_fwd_params& p, int32_t c, int32_t back, cudaStream_t s) {
   a.lens = p.lens;
   a.lens_stride = p.lens_stride;
   {
-    const kb_tensor4 ov = out_view(p.o, p.o_stride, p.H, Tq, D);
+    const kb_tensor4 ov = out_view(p.o, p.o_stride, p.H, mapTq, D);
     a.o_sb = ov.stride[0], a.o_sh = ov.stride[1], a.o_st = ov.stride[2];
     const bool lse_packed = p.lse_stride[0] == 0 && p.lse_stride[1] == 0;
-    a.lse_sb = lse_packed ? (int64_t)p.H * Tq : p.lse_stride[0];
-    a.lse_sh = lse_packed ? (int64_t)Tq : p.lse_stride[1];
+    a.lse_sb = lse_packed ? (int64_t)p.H * mapTq : p.lse_stride[0];
+    a.lse_sh = lse_packed ? (int64_t)mapTq : p.lse_stride[1];
+    if (p.cu_seqlens) a.o_sb = a.lse_sb = 0;  // the sequence's first row carries the batch offset
   }
   a.B = p.B;
   a.H = p.H;
@@ -521,6 +553,7 @@ int launch(const kb_sa_fwd_params& p, int32_t c, int32_t back, cudaStream_t s) {
   a.c = c;
   a.back = back;
   a.q_start = p.q_start;
+  a.cu = p.cu_seqlens;
   a.fd_qblocks = kb_fastdiv_make(kb_cdiv_i32(Tq, kBM * kQTiles));
   a.fd_H = kb_fastdiv_make(p.H);
   a.fd_c = kb_fastdiv_make(c);
@@ -543,8 +576,13 @@ int launch(const kb_sa_fwd_params& p, int32_t c, int32_t back, cudaStream_t s) {
 int sa_fwd_sm100(const kb_sa_fwd_params& p, int32_t c, int32_t back, cudaStream_t s) {
   if (!(p.sm_scale > 0.f) || reinterpret_cast<uintptr_t>(p.o) % 16) return KB_ERR_UNSUPPORTED;
   const bool bf16 = p.dtype == KB_BF16;
-  if (p.D == 64) return bf16 ? launch<64, true>(p, c, back, s) : launch<64, false>(p, c, back, s);
-  if (p.D == 128) return bf16 ? launch<128, true>(p, c, back, s) : launch<128, false>(p, c, back, s);
+  if (p.cu_seqlens) {
+    if (p.D == 64) return bf16 ? launch<64, true, true>(p, c, back, s) : launch<64, false, true>(p, c, back, s);
+    if (p.D == 128) return bf16 ? launch<128, true, true>(p, c, back, s) : launch<128, false, true>(p, c, back, s);
+    return KB_ERR_UNSUPPORTED;
+  }
+  if (p.D == 64) return bf16 ? launch<64, true, false>(p, c, back, s) : launch<64, false, false>(p, c, back, s);
+  if (p.D == 128) return bf16 ? launch<128, true, false>(p, c, back, s) : launch<128, false, false>(p, c, back, s);
   return KB_ERR_UNSUPPORTED;
 }
 

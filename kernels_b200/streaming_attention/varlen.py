@@ -8,9 +8,12 @@ other along the token axis, ``q`` as ``[total, H, D]`` and ``k`` / ``v`` as ``[t
 (``kernel.py:1540-1542``) applied inside every sequence, with chunks counted from the sequence's first
 row, so the result equals the padded call row for row (``tests/test_varlen_gpu.py`` checks it bit for bit).
 
-The work is done by ``kb_sa_fwd_varlen`` / ``kb_sa_bwd_varlen`` of the C-ABI library: one launch of the
-tcgen05 kernels per sequence over a strided view of the packed tensors, outputs written in place.  There is
-no other path: dtypes, head dims or layouts those kernels do not take raise.
+The work is done by ``kb_sa_fwd_varlen`` / ``kb_sa_bwd_varlen`` of the C-ABI library.  The forward is ONE
+launch of the tcgen05 kernel over all sequences (it reads every sequence's first row and length from a
+device copy of ``cu_seqlens``; the last, partial tile of a sequence is written row by row so that the next
+sequence's rows stay untouched); the backward launches its kernels once per sequence over a strided view of
+the packed tensors.  Outputs are written in place.  There is no other path: dtypes, head dims or layouts
+those kernels do not take raise.
 """
 
 import ctypes
@@ -52,7 +55,7 @@ def _params(q, k, v, cu, context_size, back_contexts, sm_scale):
 
 class _StreamingAttentionVarlen(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, q, k, v, cu_seqlens, context_size, back_contexts, sm_scale):
+    def forward(ctx, q, k, v, cu_seqlens, context_size, back_contexts, sm_scale, single_launch):
         cu, max_len = _check(q, k, v, cu_seqlens, context_size, back_contexts)
         q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
         total, H, D = q.shape
@@ -60,6 +63,8 @@ class _StreamingAttentionVarlen(torch.autograd.Function):
         lse = torch.empty((H, total), dtype=torch.float32, device=q.device)
         p = _params(q, k, v, cu, context_size, back_contexts, sm_scale)
         p.o, p.lse = o.data_ptr(), lse.data_ptr()
+        cu_dev = cu.to(q.device) if single_launch else None
+        p.cu_seqlens_dev = cu_dev.data_ptr() if single_launch else None
         with torch.cuda.device(q.device):
             rc = _lib.load().kb_sa_fwd_varlen(ctypes.byref(p), torch.cuda.current_stream(q.device).cuda_stream)
         _lib.check(rc, "kb_sa_fwd_varlen")
@@ -89,7 +94,7 @@ class _StreamingAttentionVarlen(torch.autograd.Function):
         with torch.cuda.device(q.device):
             rc = lib.kb_sa_bwd_varlen(ctypes.byref(p), torch.cuda.current_stream(q.device).cuda_stream)
         _lib.check(rc, "kb_sa_bwd_varlen")
-        return dq, dk, dv, None, None, None, None
+        return dq, dk, dv, None, None, None, None, None
 
 
 def streaming_attention_varlen(
@@ -101,15 +106,17 @@ def streaming_attention_varlen(
     back_contexts: int,
     sm_scale: Optional[float] = None,
     return_lse: bool = False,
+    single_launch: bool = True,
 ):
     """Streaming attention of every sequence of a packed batch; differentiable in q, k, v.
 
     ``q``: ``[total, H, D]``; ``k``, ``v``: ``[total, H_kv, D]`` with ``H`` a multiple of ``H_kv``;
     ``cu_seqlens``: int32 ``[B + 1]``, from 0 to ``total``.  Returns ``o`` ``[total, H, D]`` (and the base-2
     log-sum-exp ``[H, total]`` when ``return_lse``).  ``sm_scale`` defaults to ``D ** -0.5`` as in the
-    reference (``kernel.py:1622-1623``).
+    reference (``kernel.py:1622-1623``).  ``single_launch=False`` runs the forward as one launch per sequence
+    (the same bits; only worth it for a few long sequences when a device copy of ``cu_seqlens`` is unwanted).
     """
     if sm_scale is None:
         sm_scale = 1.0 / math.sqrt(q.shape[-1])
-    o, lse = _StreamingAttentionVarlen.apply(q, k, v, cu_seqlens, context_size, back_contexts, sm_scale)
+    o, lse = _StreamingAttentionVarlen.apply(q, k, v, cu_seqlens, context_size, back_contexts, sm_scale, single_launch)
     return (o, lse) if return_lse else o

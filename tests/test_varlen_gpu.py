@@ -29,8 +29,10 @@ def _cu(lens):
     (8, 2, 520, 64, 128, 1, torch.float16, [130, 520, 0, 257]),   # shared K/V heads, an empty sequence
     (2, 2, 1100, 128, 256, 2, torch.float16, [1100, 1024]),
     (3, 1, 300, 64, 10, 5, torch.bfloat16, [299, 17, 128]),
+    (2, 2, 260, 128, 32, 2, torch.float16, [5, 130, 256, 257, 1, 127, 128, 129, 0, 260]),  # every kind of last tile
 ])
-def test_packed_equals_padded_bitwise(H, Hk, T, D, c, back, dtype, lens):
+@pytest.mark.parametrize("single_launch", [True, False])
+def test_packed_equals_padded_bitwise(H, Hk, T, D, c, back, dtype, lens, single_launch):
     from kernels_b200.streaming_attention import streaming_attention, streaming_attention_varlen
 
     B = len(lens)
@@ -48,14 +50,15 @@ def test_packed_equals_padded_bitwise(H, Hk, T, D, c, back, dtype, lens):
 
     qs, ks, vs = (_pack(t, lens).requires_grad_() for t in (q, k, v))
     n0 = _lib.launch_count()
-    out, lse = streaming_attention_varlen(qs, ks, vs, _cu(lens), c, back, return_lse=True)
+    out, lse = streaming_attention_varlen(qs, ks, vs, _cu(lens), c, back, return_lse=True, single_launch=single_launch)
     n1 = _lib.launch_count()
     out.backward(_pack(do, lens))
     torch.cuda.synchronize()
     n2 = _lib.launch_count()
     _lib.check_device_status()
     live = sum(1 for L in lens if L > 0)
-    assert n1 - n0 == live and n2 - n1 == 3 * live  # forward; delta + main + dQ kernels, per sequence
+    # forward: one launch for the batch or one per sequence; backward: delta + main + dQ kernels per sequence
+    assert n1 - n0 == (1 if single_launch else live) and n2 - n1 == 3 * live
 
     assert out.shape == qs.shape and lse.shape == (H, sum(lens))
     assert torch.equal(out, _pack(out_pad.detach(), lens))
