@@ -198,9 +198,11 @@ KB_API int kb_sa_bwd_noalloc(const kb_sa_bwd_params* p, void* stream);
  * Streaming attention over a PACKED batch (no counterpart in the reference, whose callers hold padded
  * [B, T] batches with `lens`, kernel.py:1586-1652): the sequences lie one after the other along the token
  * axis, q / o / dq as [total, H, D], k / v / dk / dv as [total, H_kv, D], lse as [H, total]; sequence b owns
- * the rows [cu_seqlens[b], cu_seqlens[b + 1]).  No padded row is read, computed or written.  Each sequence is
- * one launch of the kernels above over a strided view (batch 1, T = its length, tiles counted from its own
- * first row), so the results equal those of the padded call row for row.  `cu_seqlens` is read on the HOST.
+ * the rows [cu_seqlens[b], cu_seqlens[b + 1]).  No padded row is read, computed or written.  Tiles are counted
+ * from every sequence's own first row, so the results equal those of the padded call row for row.  The forward
+ * is one launch over all sequences when `cu_seqlens_dev` is given, else one launch per sequence over a strided
+ * view (batch 1, T = its length); the backward launches its kernels per sequence.  `cu_seqlens` is read on the
+ * HOST in every case.
  * tcgen05 kernels only (f16 / bf16, D 64 or 128); the backward needs `delta_ws` (H * max_len floats) and
  * `ds_ws` (kb_sa_bwd_workspace_bytes(1, H, max_len, ...) bytes), both reused from sequence to sequence.
  */

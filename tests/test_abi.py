@@ -249,3 +249,28 @@ def test_streaming_step_start_is_validated_without_a_gpu():
     assert lib.kb_sa_fwd(ctypes.byref(p), None) == 1                 # no query row left
     p.q_start, p.dtype = 4, _lib.KB_F32
     assert lib.kb_sa_fwd(ctypes.byref(p), None) == 2                 # tcgen05 kernels only
+
+
+def test_packed_single_launch_arguments_are_validated_without_a_gpu():
+    lib = _lib.load()
+    buf = (ctypes.c_uint16 * 4096)()
+    ptr = ctypes.cast(buf, ctypes.c_void_p)
+    cu = (ctypes.c_int32 * 3)(0, 5, 8)
+    p = _lib.SaFwdParams()
+    p.B, p.H, p.T, p.D, p.dtype, p.context_size, p.back_contexts = 2, 1, 5, 64, _lib.KB_F16, 4, 1
+    for t in (p.q, p.k, p.v):
+        t.data = ptr
+        t.stride[0], t.stride[1], t.stride[2], t.stride[3] = 0, 64, 64, 1
+    p.o = ptr
+    p.sm_scale = 0.125
+    p.cu_seqlens = ctypes.cast(cu, ctypes.c_void_p)
+    p.total_rows = 4
+    assert lib.kb_sa_fwd(ctypes.byref(p), None) == 1                 # fewer rows than the longest sequence
+    p.total_rows, p.q_start = 8, 1
+    assert lib.kb_sa_fwd(ctypes.byref(p), None) == 1                 # a packed batch has no streaming step
+    p.q_start = 0
+    p.lens, p.lens_stride = ctypes.cast(cu, ctypes.c_void_p), 1
+    assert lib.kb_sa_fwd(ctypes.byref(p), None) == 1                 # nor `lens`: the offsets give the lengths
+    p.lens, p.dtype = None, _lib.KB_F32
+    assert lib.kb_sa_fwd(ctypes.byref(p), None) == 2                 # tcgen05 kernels only
+    assert lib.kb_fa_fwd(ctypes.byref(p), None) in (1, 2)            # the dense kernel takes no packed batch
