@@ -231,6 +231,12 @@ typedef struct kb_sa_varlen_params {
    * kernel reads a sequence's first row and length from it) instead of one launch per sequence (the host copy
    * is still read, for the checks and the longest sequence).  The backward still launches per sequence. */
   const int32_t* cu_seqlens_dev;
+  /* Backward only.  0 or 1: the per-sequence launches follow one another on `stream`.  2 .. 8: they are spread
+   * over that many streams of the library's own (made on the first such call on a device), forked from and
+   * joined back into `stream`, so that short sequences, each of which fills only a few SMs, run side by side.
+   * Every lane needs scratch of its own: `delta_ws` must then hold lanes * H * max_len floats and `ds_ws`
+   * lanes times the bytes of one lane. */
+  uint32_t lanes;
 } kb_sa_varlen_params;
 
 KB_API int kb_sa_fwd_varlen(const kb_sa_varlen_params* p, void* stream);

@@ -74,7 +74,7 @@ class SaVarlenParams(C.Structure):
         ("B", C.c_int32), ("H", C.c_int32), ("H_kv", C.c_int32), ("D", C.c_int32),
         ("dtype", C.c_int32), ("context_size", C.c_int32), ("back_contexts", C.c_int32),
         ("sm_scale", C.c_float), ("flags", C.c_uint32), ("status", C.c_void_p),
-        ("cu_seqlens_dev", C.c_void_p),
+        ("cu_seqlens_dev", C.c_void_p), ("lanes", C.c_uint32),
     ]
 
 

@@ -1,6 +1,7 @@
 // extern "C" surface of the library (declared in include/kernels_b200.h): argument
 // validation, kernel-family selection and the host-side schedule planner.
 #include <atomic>
+#include <mutex>
 #include <cstdio>
 #include <cstring>
 
@@ -231,15 +232,64 @@ int kb_sa_fwd_varlen(const kb_sa_varlen_params* p, void* stream) {
   return KB_OK;
 }
 
+// Lanes of the packed backward: streams of the library's own on which the per-sequence launches of different
+// sequences run side by side (a short sequence fills only a few SMs), each with its own slice of the scratch.
+// Made once per device; the mutex also keeps two host threads from interleaving their use of the fork event.
+namespace {
+constexpr int kMaxLanes = 8;
+struct LanePool {
+  cudaStream_t lane[kMaxLanes];
+  cudaEvent_t fork, join[kMaxLanes];
+};
+std::mutex g_lane_mutex;
+LanePool* g_lane_pool[64] = {};
+LanePool* lane_pool_locked() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  if (g_lane_pool[dev]) return g_lane_pool[dev];
+  LanePool* lp = new LanePool();
+  bool ok = cudaEventCreateWithFlags(&lp->fork, cudaEventDisableTiming) == cudaSuccess;
+  for (int i = 0; ok && i < kMaxLanes; ++i)
+    ok = cudaStreamCreateWithFlags(&lp->lane[i], cudaStreamNonBlocking) == cudaSuccess &&
+         cudaEventCreateWithFlags(&lp->join[i], cudaEventDisableTiming) == cudaSuccess;
+  if (!ok) {
+    delete lp;  // a device that cannot give a handful of streams: the caller falls back to one lane
+    return nullptr;
+  }
+  return g_lane_pool[dev] = lp;
+}
+}  // namespace
+
 int kb_sa_bwd_varlen(const kb_sa_varlen_params* p, void* stream) {
   int rc = check_varlen(p, true);
   if (rc || p->B == 0) return rc;
   const int32_t Hk = p->H_kv > 0 ? p->H_kv : p->H, D = p->D;
   const int64_t total = p->cu_seqlens[p->B];
+  if (p->lanes > (uint32_t)kMaxLanes) return KB_ERR_BAD_ARGUMENT;
+  int32_t max_len = 0;
+  for (int32_t b = 0; b < p->B; ++b) max_len = kb_max_i32(max_len, p->cu_seqlens[b + 1] - p->cu_seqlens[b]);
+  int lanes = p->lanes > 1 ? (int)p->lanes : 1;
+  std::unique_lock<std::mutex> lock(g_lane_mutex, std::defer_lock);
+  LanePool* pool = nullptr;
+  cudaStream_t caller = static_cast<cudaStream_t>(stream);
+  if (lanes > 1) {
+    lock.lock();
+    pool = lane_pool_locked();
+    if (!pool) {
+      lanes = 1;
+      lock.unlock();
+    } else {
+      KB_CUDA_TRY(cudaEventRecord(pool->fork, caller));
+      for (int i = 0; i < lanes; ++i) KB_CUDA_TRY(cudaStreamWaitEvent(pool->lane[i], pool->fork, 0));
+    }
+  }
+  const uint64_t ds_lane_bytes = (p->ds_ws_bytes / (uint64_t)lanes) & ~(uint64_t)255;
+  int32_t live = 0;
   for (int32_t b = 0; b < p->B; ++b) {
     const int64_t r0 = p->cu_seqlens[b];
     const int32_t len = p->cu_seqlens[b + 1] - p->cu_seqlens[b];
     if (len == 0) continue;
+    const int lane = live++ % lanes;
     kb_sa_bwd_params g = {};
     g.q = packed_view(p->q, r0, p->H, D);
     g.k = packed_view(p->k, r0, Hk, D);
@@ -253,14 +303,23 @@ int kb_sa_bwd_varlen(const kb_sa_varlen_params* p, void* stream) {
     g.dk = static_cast<uint16_t*>(p->dk) + r0 * Hk * D;
     g.dv = static_cast<uint16_t*>(p->dv) + r0 * Hk * D;
     g.dkv_stride[0] = (int64_t)len * Hk * D, g.dkv_stride[1] = D, g.dkv_stride[2] = (int64_t)Hk * D;
-    g.delta_ws = p->delta_ws, g.ds_ws = p->ds_ws, g.ds_ws_bytes = p->ds_ws_bytes;
+    g.delta_ws = p->delta_ws + (int64_t)lane * p->H * max_len;
+    g.ds_ws = static_cast<uint8_t*>(p->ds_ws) + (uint64_t)lane * ds_lane_bytes, g.ds_ws_bytes = ds_lane_bytes;
     g.B = 1, g.H = p->H, g.T = len, g.D = D, g.H_kv = Hk;
     g.dtype = p->dtype, g.context_size = p->context_size, g.back_contexts = p->back_contexts;
     g.sm_scale = p->sm_scale, g.flags = p->flags & ~KB_FLAG_BWD_TWO_PASS, g.status = p->status;
-    rc = kb_sa_bwd(&g, stream);
-    if (rc) return rc;
+    rc = kb_sa_bwd(&g, pool ? pool->lane[lane] : caller);
+    if (rc) break;
   }
-  return KB_OK;
+  if (pool) {
+    // the caller's stream continues after every lane, also when a launch failed half way
+    for (int i = 0; i < lanes; ++i) {
+      const bool ok = cudaEventRecord(pool->join[i], pool->lane[i]) == cudaSuccess &&
+                      cudaStreamWaitEvent(caller, pool->join[i], 0) == cudaSuccess;
+      if (!ok && !rc) rc = KB_ERR_LAUNCH;
+    }
+  }
+  return rc;
 }
 
 uint64_t kb_sa_bwd_workspace_bytes(int32_t B, int32_t H, int32_t T, int32_t D, int32_t dtype, int32_t context_size,

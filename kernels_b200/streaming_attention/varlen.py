@@ -12,8 +12,9 @@ The work is done by ``kb_sa_fwd_varlen`` / ``kb_sa_bwd_varlen`` of the C-ABI lib
 launch of the tcgen05 kernel over all sequences (it reads every sequence's first row and length from a
 device copy of ``cu_seqlens``; the last, partial tile of a sequence is written row by row so that the next
 sequence's rows stay untouched); the backward launches its kernels once per sequence over a strided view of
-the packed tensors.  Outputs are written in place.  There is no other path: dtypes, head dims or layouts
-those kernels do not take raise.
+the packed tensors, spread over up to eight streams of the library's own ("lanes", each with its own scratch)
+so that short sequences run side by side.  Outputs are written in place.  There is no other path: dtypes,
+head dims or layouts those kernels do not take raise.
 """
 
 import ctypes
@@ -23,7 +24,7 @@ from typing import Optional
 import torch
 
 from .. import _lib
-from .kernel import _clamp_i32
+from .kernel import _clamp_i32, _free_bytes
 
 
 def _check(q, k, v, cu_seqlens, context_size, back_contexts):
@@ -82,15 +83,24 @@ class _StreamingAttentionVarlen(torch.autograd.Function):
         do = do.to(q.dtype).contiguous()
         dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
         lib = _lib.load()
-        # scratch of the longest sequence, reused from sequence to sequence (the launches are stream-ordered)
+        # scratch of the longest sequence, reused from sequence to sequence (the launches of a lane are
+        # stream-ordered); with more than a few sequences the launches are spread over lanes that run side by
+        # side, each with scratch of its own, as long as that stays a small part of the free memory
         ws_bytes = int(lib.kb_sa_bwd_workspace_bytes(1, H, max(ctx.max_len, 1), D, _lib.dtype_code(q.dtype),
                                                      _clamp_i32(context_size), _clamp_i32(back_contexts)))
-        delta = torch.empty(H * max(ctx.max_len, 1), dtype=torch.float32, device=q.device)
-        ds_ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=q.device)
+        ws_bytes = (ws_bytes + 255) // 256 * 256
+        n_seq = ctx.cu.numel() - 1
+        lanes = 1
+        if n_seq >= 4:
+            lanes = min(8, n_seq // 2)
+            while lanes > 1 and lanes * ws_bytes > _free_bytes(q.device) // 8:
+                lanes -= 1
+        delta = torch.empty(lanes * H * max(ctx.max_len, 1), dtype=torch.float32, device=q.device)
+        ds_ws = torch.empty(max(lanes * ws_bytes, 256), dtype=torch.uint8, device=q.device)
         p = _params(q, k, v, ctx.cu, context_size, back_contexts, sm_scale)
         p.o, p.lse, p.d_o = o.data_ptr(), lse.data_ptr(), do.data_ptr()
         p.dq, p.dk, p.dv = dq.data_ptr(), dk.data_ptr(), dv.data_ptr()
-        p.delta_ws, p.ds_ws, p.ds_ws_bytes = delta.data_ptr(), ds_ws.data_ptr(), ws_bytes
+        p.delta_ws, p.ds_ws, p.ds_ws_bytes, p.lanes = delta.data_ptr(), ds_ws.data_ptr(), lanes * ws_bytes, lanes
         with torch.cuda.device(q.device):
             rc = lib.kb_sa_bwd_varlen(ctypes.byref(p), torch.cuda.current_stream(q.device).cuda_stream)
         _lib.check(rc, "kb_sa_bwd_varlen")
