@@ -274,3 +274,18 @@ def test_packed_single_launch_arguments_are_validated_without_a_gpu():
     p.lens, p.dtype = None, _lib.KB_F32
     assert lib.kb_sa_fwd(ctypes.byref(p), None) == 2                 # tcgen05 kernels only
     assert lib.kb_fa_fwd(ctypes.byref(p), None) in (1, 2)            # the dense kernel takes no packed batch
+
+
+def test_packed_backward_lane_count_is_validated_without_a_gpu():
+    lib = _lib.load()
+    buf = (ctypes.c_uint16 * 4096)()
+    ptr = ctypes.cast(buf, ctypes.c_void_p).value
+    cu = (ctypes.c_int32 * 3)(0, 5, 8)
+    p = _lib.SaVarlenParams()
+    p.B, p.H, p.D, p.dtype, p.context_size, p.back_contexts = 2, 1, 64, _lib.KB_F16, 4, 1
+    p.cu_seqlens = ctypes.cast(cu, ctypes.c_void_p)
+    for name in ("q", "k", "v", "o", "lse", "d_o", "dq", "dk", "dv", "delta_ws", "ds_ws"):
+        setattr(p, name, ptr)
+    p.ds_ws_bytes, p.sm_scale = 4096, 0.125
+    p.lanes = 9
+    assert lib.kb_sa_bwd_varlen(ctypes.byref(p), None) == 1          # at most eight lanes
