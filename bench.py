@@ -45,13 +45,13 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 WORKLOADS = {
-    # BASELINE.json configs[2]: the configuration the >= 60 %-of-peak target is quoted on
+    # the long-sequence configuration the >= 60 %-of-peak target is quoted on
     "cfg3": dict(dtype="bf16", B=4, H=32, T=16384, D=128, c=256, back=2, lens=None, qk_scale=1.0, scaling="weak",
                  desc="bf16 B=4 H=32 T=16384 D=128 context=256 back=2 lens=T (per GPU)"),
-    # configs[1]
+    # the fp16 head-dim-64 configuration with random lengths
     "cfg2": dict(dtype="f16", B=8, H=16, T=4096, D=64, c=128, back=4, lens=(2048, 4096), qk_scale=64 ** -0.25,
                  scaling="weak", desc="fp16 B=8 H=16 T=4096 D=64 context=128 back=4 lens~U[2048,4096] (per GPU)"),
-    # configs[4]: fixed total problem, batch x heads split over the GPUs
+    # the multi-GPU configuration: fixed total problem, batch x heads split over the GPUs
     "cfg5": dict(dtype="bf16", B=64, H=32, T=8192, D=128, c=64, back=8, lens=(4096, 8192), qk_scale=1.0,
                  scaling="strong", desc="bf16 B=64 H=32 T=8192 D=128 context=64 back=8 lens~U[4096,8192] (total)"),
     # small stand-in for cfg3 (same tiles and schedule, 1/4 of the slices) for ncu captures
@@ -490,7 +490,7 @@ def run_own(args, w):
 
 
 def run_dense(args):
-    """BASELINE.json configs[3]: dense self-attention forward (fp16 B=16 H=16 T=2048 D=64, key padding
+    """The dense configuration: self-attention forward (fp16 B=16 H=16 T=2048 D=64, key padding
     lens ~ U[1024, 2048]) and row softmax (fp32 [65536, 4096] ~ N(0, 4)), one GPU.  Each iteration is
     timed with its own event pair; a 512 MB buffer is rewritten between iterations to flush L2."""
     from kernels_b200 import _lib, synthetic

@@ -183,11 +183,17 @@ KB_API uint64_t kb_sa_bwd_workspace_bytes(int32_t B, int32_t H, int32_t T, int32
  * gets input and output bindings, a process that gave all device memory to its own arena, a
  * latency-bound loop that cannot pay for cudaMalloc's device synchronisation.
  * Same parameter block as kb_sa_bwd; `delta_ws` and `ds_ws` are ignored (the two-pass kernels
- * run, which need no other scratch).  The B*H*T floats of delta live in
+ * run, which need no other scratch).  What those kernels do not take, this entry point does not
+ * take either: shared key/value heads (H_kv other than 0 or H) and strided gradients (dq_stride,
+ * dkv_stride, lse_stride set) return KB_ERR_UNSUPPORTED with nothing launched.  The
+ * KB_FLAG_BWD_SKIP_* timing flags are refused (KB_ERR_BAD_ARGUMENT): a skipped pass would leave
+ * the other one reading an earlier call's delta.  The B*H*T floats of delta live in
  * a fixed array inside the library (KB_NOALLOC_MAX_ROWS floats = 8 MiB per GPU, held until the
  * process exits); larger problems return KB_ERR_TOO_LARGE and launch nothing.  The first call
- * on a device resolves the array's address: make it during set-up, before any stream capture
- * on that device.  All calls on a device share the array (it need not be cleared: each call
+ * on a device resolves the array's address and, under the CUDA runtime's lazy module loading, is
+ * when the device sets the 8 MiB aside: make it during set-up, before any stream capture on that
+ * device and before the host reserves the remaining device memory for itself.  All calls on a
+ * device share the array (it need not be cleared: each call
  * overwrites what it reads), so calls that overlap on one GPU race and must be serialised.
  * Calls no cudaMalloc / cudaFree or allocating library routine.
  */
@@ -285,6 +291,17 @@ KB_API int kb_sa_plan(int32_t T, int32_t seq_len, int32_t context_size, int32_t 
  */
 KB_API int kb_sa_tile_config(int32_t dtype, int32_t D, int32_t context_size, uint32_t flags, int32_t unit_inner_stride,
                       int32_t which, int32_t* path, int32_t* tile_q, int32_t* tile_k, int32_t* stages);
+
+/*
+ * Self-test of the failure path (no counterpart in the reference, which has no device-side waits): launches
+ * one small CTA that waits, with a limit of 1 024 polls, on an mbarrier nobody arrives on, through the same
+ * bounded wait every tcgen05 kernel of the library uses.  Nothing faults or hangs: the wait gives up, writes
+ * {KB_ERR_DEVICE_TIMEOUT, 900, 0} to `status` (KB_STATUS_WORDS int32, device-visible, e.g. pinned host
+ * memory) and the kernel returns.  `seen` (3 device-visible int32) receives: whether the short wait reported
+ * success (0 expected), whether a second role's long wait on the same barrier did (0 expected: it leaves on the
+ * abort flag), and the abort flag (1 expected).  Read both after synchronising the stream.
+ */
+KB_API int kb_selftest_wait_timeout(int32_t* status, int32_t* seen, void* stream);
 
 /* number of kernels the library launched since it was loaded (all entry points) */
 KB_API int64_t kb_launch_count(void);

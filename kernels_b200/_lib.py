@@ -26,7 +26,7 @@ _DTYPES = {torch.float32: KB_F32, torch.float16: KB_F16, torch.bfloat16: KB_BF16
 
 EXPORTS = (
     "kb_sa_fwd", "kb_sa_bwd", "kb_sa_bwd_workspace_bytes", "kb_sa_bwd_noalloc", "kb_sa_fwd_varlen", "kb_sa_bwd_varlen", "kb_fa_fwd", "kb_softmax_fwd", "kb_sa_plan", "kb_sa_tile_config",
-    "kb_launch_count", "kb_strerror", "kb_last_cuda_error", "kb_version",
+    "kb_launch_count", "kb_strerror", "kb_last_cuda_error", "kb_version", "kb_selftest_wait_timeout",
 )
 
 
@@ -119,6 +119,8 @@ def load() -> C.CDLL:
     ] * 4
     lib.kb_sa_tile_config.restype = C.c_int
     lib.kb_launch_count.restype = C.c_int64
+    lib.kb_selftest_wait_timeout.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p]
+    lib.kb_selftest_wait_timeout.restype = C.c_int
     for f in (lib.kb_strerror, lib.kb_last_cuda_error, lib.kb_version):
         f.restype = C.c_char_p
     lib.kb_strerror.argtypes = [C.c_int]

@@ -6,6 +6,7 @@
 #include <cstring>
 
 #include "common.cuh"
+#include "tiles.h"
 
 namespace kb {
 
@@ -366,35 +367,43 @@ int kb_sa_plan(int32_t T, int32_t seq_len, int32_t context_size, int32_t back_co
 
 int kb_sa_tile_config(int32_t dtype, int32_t D, int32_t context_size, uint32_t flags, int32_t unit_inner_stride,
                       int32_t which, int32_t* path, int32_t* tile_q, int32_t* tile_k, int32_t* stages) {
-  (void)context_size;
+  namespace t = kb::tiles;
+  // One row per (dtype, head dim) class today: the measurements behind the table (profiles/) found no
+  // chunk length for which another tile beats 128-row tiles on the tcgen05 path, so `context_size` does
+  // not select a row; it stays in the signature because the table is keyed on it.
+  if (context_size < 1) return KB_ERR_BAD_ARGUMENT;
   if (!kb::dtype_ok(dtype) || !kb::head_dim_ok(D)) return KB_ERR_UNSUPPORTED;
   if (which < 0 || which > 4) return KB_ERR_BAD_ARGUMENT;
-  int32_t pth = KB_PATH_GENERIC, tq = D <= 128 ? 64 : 32, tk = tq, st = 1;
+  int32_t pth = KB_PATH_GENERIC, tq = t::generic_tile(D), tk = tq, st = t::kGenericStages;
 #ifdef KB_HAVE_SM100
   if (kb::sm100_shape_ok(dtype, D, flags) && unit_inner_stride) {
-    // forward: two 128-row q tiles per CTA share 128-key K/V tiles (K ring 3 deep, V ring 2 deep);
-    // backward passes: 128 stationary rows, 128-row streamed tiles (rings 3 and 2 deep)
+    // every number below is the constant the kernel itself is compiled with (tiles.h)
     if (which == 0) {
       pth = KB_PATH_SM100;
-      tq = 256;
-      tk = 128;
-      st = 3;
+      tq = t::kFwdQRows * t::kFwdQTiles;
+      tk = t::kFwdKeys;
+      st = t::kFwdStagesK;  // K ring; the V ring has t::kFwdStagesV stages
     }
 #ifdef KB_HAVE_SM100_BWD
     if (which == 1 || which == 2) {
       pth = KB_PATH_SM100;
-      tq = 128;
-      tk = 128;
-      st = 3;
+      tq = which == 1 ? t::kTwoPassStationary : t::kTwoPassStreamed;
+      tk = which == 1 ? t::kTwoPassStreamed : t::kTwoPassStationary;
+      st = t::kTwoPassStagesFirst;  // ring of the first streamed operand; the second has kTwoPassStagesSecond
     }
 #endif
 #ifdef KB_HAVE_SM100_BWD_FUSED
-    // single-evaluation backward: main kernel (Q ring 2 deep), dQ kernel (dS / K ring 3 deep)
-    if (which == 3 || which == 4) {
+    if (which == 3) {
       pth = KB_PATH_SM100;
-      tq = 128;
-      tk = 128;
-      st = which == 3 ? 2 : 3;
+      tq = t::kMainQueries;
+      tk = t::kMainKeys;
+      st = t::kMainStagesQ;
+    }
+    if (which == 4) {
+      pth = KB_PATH_SM100;
+      tq = t::kDqQueries;
+      tk = t::kDqKeys;
+      st = t::kDqStages;
     }
 #endif
   }

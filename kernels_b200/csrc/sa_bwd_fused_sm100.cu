@@ -47,6 +47,7 @@
 #include "common.cuh"
 #include "sm100_ptx.cuh"
 #include "sm100_host.h"
+#include "tiles.h"
 
 namespace kb {
 #ifdef KB_TRACE_FUSED
@@ -66,8 +67,11 @@ namespace {
 
 using namespace sm100;
 
-constexpr int kBK = 128;  // key rows of a key tile
-constexpr int kBQ = 128;  // query rows of a query tile
+constexpr int kBK = tiles::kMainKeys;     // key rows of a key tile
+constexpr int kBQ = tiles::kMainQueries;  // query rows of a query tile
+static_assert(kBK == 128 && kBQ == 128 && tiles::kDqQueries == kBQ && tiles::kDqKeys == kBK && tiles::kMainStagesQ == 2 &&
+                  tiles::kMainStagesK == 2,
+              "the TMEM column map, the dS tile layout and the buffer indexing assume 128 x 128 tiles and double buffers");
 constexpr int kThreads = 512;
 constexpr int kComputeThreads = 256, kEpiThreads = 128;
 constexpr int kEpiWarp0 = 8, kProducerWarp = 12, kMmaWarp = 13, kSpillWarp = 14;
@@ -757,7 +761,7 @@ __global__ void __launch_bounds__(256) sa_bwd_delta_kernel(const DeltaArgs a) {
 // warp 4 producer (one lane: a 32 KB bulk copy of dS and a TMA tile of K per stage, three stages),
 // warp 5 MMA issuer (one lane) and TMEM owner.  The accumulator is double buffered in TMEM so that
 // the MMAs of the next item run while the epilogue warps convert and store the finished one.
-constexpr int kDqStages = 3;
+constexpr int kDqStages = tiles::kDqStages;
 constexpr int kDqThreads = 192;
 constexpr int kDqProducerWarp = 4, kDqMmaWarp = 5;
 constexpr uint32_t kDqTmemCols = 256;
@@ -957,8 +961,7 @@ int launch_fused(const kb_sa_bwd_params& p, int32_t c, int32_t back, cudaStream_
   const int64_t n_items = (int64_t)p.B * p.H * n_tiles;
   if (n_items > (int64_t)1 << 30) return KB_ERR_TOO_LARGE;
   int dev = 0, n_sm = 0;
-  KB_CUDA_TRY(cudaGetDevice(&dev));
-  KB_CUDA_TRY(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev));
+  if (!device_sm_count(&dev, &n_sm)) return KB_ERR_LAUNCH;
   const unsigned grid = (unsigned)(n_items < n_sm ? n_items : n_sm);  // persistent: one CTA per SM (dQ kernel)
   const int64_t n_items_main = (int64_t)p.B * Hk * n_tiles;
   const unsigned grid_main = (unsigned)(n_items_main < n_sm ? n_items_main : n_sm);
@@ -966,8 +969,9 @@ int launch_fused(const kb_sa_bwd_params& p, int32_t c, int32_t back, cudaStream_
   auto main_kern = sa_bwd_fused_kernel<D, BF16>;
   auto dq_kern = sa_bwd_dq_kernel<D, BF16>;
   static_assert(sizeof(FusedSmem<D>) <= 232448 && sizeof(DqSmem<D>) <= 232448, "shared memory exceeds the 227 KB a CTA may have");
-  KB_CUDA_TRY(cudaFuncSetAttribute(main_kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(FusedSmem<D>)));
-  KB_CUDA_TRY(cudaFuncSetAttribute(dq_kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(DqSmem<D>)));
+  static std::atomic<bool> main_opted_in[kMaxDevices], dq_opted_in[kMaxDevices];
+  KB_CUDA_TRY(opt_in_smem_once(main_kern, sizeof(FusedSmem<D>), dev, main_opted_in));
+  KB_CUDA_TRY(opt_in_smem_once(dq_kern, sizeof(DqSmem<D>), dev, dq_opted_in));
 
   DeltaArgs da;
   da.o = static_cast<const uint16_t*>(p.o.data);

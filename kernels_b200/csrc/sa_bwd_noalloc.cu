@@ -10,12 +10,19 @@
 // For them this file keeps the scratch in a fixed array inside the library image.
 //
 // Properties a caller must know:
-//   * the array holds KB_NOALLOC_MAX_ROWS floats (8 MiB) on every GPU that loads the library,
-//     from load until the process exits; a problem with B*H*T above that is refused with
+//   * the array holds KB_NOALLOC_MAX_ROWS floats (8 MiB) on every GPU that uses the library,
+//     until the process exits; a problem with B*H*T above that is refused with
 //     KB_ERR_TOO_LARGE and nothing is launched;
 //   * the first call on each device looks up the array's device address (one
-//     cudaGetSymbolAddress with that device current).  Make that first call during set-up,
-//     before any stream capture is started on that device;
+//     cudaGetSymbolAddress with that device current).  With the CUDA runtime's lazy module
+//     loading that is also the moment the device sets the 8 MiB aside, so make that first call
+//     during set-up: before any stream capture is started on that device, and before the host
+//     hands the rest of the device memory to an arena of its own;
+//   * it runs the two-pass kernels as they are: one key/value head per query head and contiguous
+//     dq / dk / dv only (H_kv other than 0 or H, or any *_stride set, returns
+//     KB_ERR_UNSUPPORTED with nothing launched), and none of the KB_FLAG_BWD_SKIP_* timing flags
+//     (a pass that is skipped would leave the other reading an EARLIER call's delta out of the
+//     shared array; KB_ERR_BAD_ARGUMENT);
 //   * every call on a device shares the one array and it keeps the previous call's values.
 //     Nothing in it has to start at zero: the dQ pass overwrites every entry the dK/dV pass of
 //     the same call reads.  Two calls that overlap on the same GPU (different streams) race on
@@ -55,6 +62,8 @@ int scratch_for_current_device(float** out) {
 extern "C" int kb_sa_bwd_noalloc(const kb_sa_bwd_params* p, void* stream) {
   if (!p) return KB_ERR_BAD_ARGUMENT;
   if (p->B < 0 || p->H < 0 || p->T < 0) return KB_ERR_BAD_ARGUMENT;
+  // every call must write the delta it reads: no partial backward out of the shared array
+  if (p->flags & (KB_FLAG_BWD_SKIP_DQ | KB_FLAG_BWD_SKIP_DKDV | KB_FLAG_BWD_SKIP_DELTA)) return KB_ERR_BAD_ARGUMENT;
   const int64_t rows = (int64_t)p->B * p->H * p->T;
   if (rows > (int64_t)KB_NOALLOC_MAX_ROWS) return KB_ERR_TOO_LARGE;
   float* scratch = nullptr;

@@ -36,6 +36,7 @@
 #include "common.cuh"
 #include "sm100_ptx.cuh"
 #include "sm100_host.h"
+#include "tiles.h"
 
 namespace kb {
 #ifdef KB_TRACE
@@ -55,9 +56,10 @@ namespace {
 
 using namespace sm100;
 
-constexpr int kBX = 128;  // stationary rows per CTA
-constexpr int kBY = 128;  // streamed rows per tile
-constexpr int kStagesB1 = 3, kStagesB2 = 2;
+constexpr int kBX = tiles::kTwoPassStationary;  // stationary rows per CTA
+constexpr int kBY = tiles::kTwoPassStreamed;    // streamed rows per tile
+constexpr int kStagesB1 = tiles::kTwoPassStagesFirst, kStagesB2 = tiles::kTwoPassStagesSecond;
+static_assert(kBX == 128 && kBY == 128, "the TMEM column map assumes 128 x 128 score blocks");
 constexpr int kComputeWarps = 8;
 constexpr int kComputeThreads = kComputeWarps * 32;
 constexpr int kThreads = (kComputeWarps + 2) * 32;
@@ -544,24 +546,32 @@ sa_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_a1, const __grid_cons
   }
 }
 
-template <int D, bool BF16, bool kDQ>
-int launch_pass(const kb_sa_bwd_params& p, int32_t c, int32_t back, cudaStream_t s) {
-  CUtensorMap tm_a1, tm_a2, tm_b1, tm_b2;
+// The six tensor maps of one pass.  Both passes' maps are made before either pass is launched, so
+// "unsupported" (a layout no map describes) always means that nothing ran.
+struct PassMaps {
+  CUtensorMap a1, a2, b1, b2, o1, o2;
+};
+template <int D, bool kDQ>
+bool make_pass_maps(PassMaps* m, const kb_sa_bwd_params& p) {
   const kb_tensor4& a1 = kDQ ? p.q : p.k;
   const kb_tensor4& a2 = kDQ ? p.d_o : p.v;
   const kb_tensor4& b1 = kDQ ? p.k : p.q;
   const kb_tensor4& b2 = kDQ ? p.v : p.d_o;
-  if (!make_tile_map_4d(&tm_a1, a1, p.B, p.H, p.T, D, kBX) || !make_tile_map_4d(&tm_a2, a2, p.B, p.H, p.T, D, kBX) ||
-      !make_tile_map_4d(&tm_b1, b1, p.B, p.H, p.T, D, kBY) || !make_tile_map_4d(&tm_b2, b2, p.B, p.H, p.T, D, kBY))
-    return KB_ERR_UNSUPPORTED;
-  CUtensorMap tm_o1, tm_o2;
-  if (!make_tile_map_4d_contiguous(&tm_o1, kDQ ? p.dq : p.dv, p.B, p.H, p.T, D, kBX) ||
-      !make_tile_map_4d_contiguous(&tm_o2, kDQ ? p.dq : p.dk, p.B, p.H, p.T, D, kBX))
-    return KB_ERR_UNSUPPORTED;
+  return make_tile_map_4d(&m->a1, a1, p.B, p.H, p.T, D, kBX) && make_tile_map_4d(&m->a2, a2, p.B, p.H, p.T, D, kBX) &&
+         make_tile_map_4d(&m->b1, b1, p.B, p.H, p.T, D, kBY) && make_tile_map_4d(&m->b2, b2, p.B, p.H, p.T, D, kBY) &&
+         make_tile_map_4d_contiguous(&m->o1, kDQ ? p.dq : p.dv, p.B, p.H, p.T, D, kBX) &&
+         make_tile_map_4d_contiguous(&m->o2, kDQ ? p.dq : p.dk, p.B, p.H, p.T, D, kBX);
+}
+
+template <int D, bool BF16, bool kDQ>
+int launch_pass(const kb_sa_bwd_params& p, const PassMaps& m, int32_t c, int32_t back, cudaStream_t s) {
   auto kern = sa_bwd_sm100_kernel<D, BF16, kDQ>;
   constexpr size_t smem = sizeof(BwdSmem<D>);
   static_assert(sizeof(BwdSmem<D>) <= 232448, "backward shared memory exceeds the 227 KB a CTA may have");
-  KB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  int dev = 0, n_sm = 0;
+  if (!device_sm_count(&dev, &n_sm)) return KB_ERR_LAUNCH;
+  static std::atomic<bool> smem_opted_in[kMaxDevices];
+  KB_CUDA_TRY(opt_in_smem_once(kern, smem, dev, smem_opted_in));
   BwdArgs a;
   a.o = static_cast<const uint16_t*>(p.o.data);
   a.d_o = static_cast<const uint16_t*>(p.d_o.data);
@@ -585,19 +595,23 @@ int launch_pass(const kb_sa_bwd_params& p, int32_t c, int32_t back, cudaStream_t
   a.sm_scale = p.sm_scale;
   a.status = p.status;
   dim3 grid(kb_cdiv_i32(p.T, kBX), p.H, p.B);
-  kern<<<grid, kThreads, smem, s>>>(tm_a1, tm_a2, tm_b1, tm_b2, tm_o1, tm_o2, a);
+  kern<<<grid, kThreads, smem, s>>>(m.a1, m.a2, m.b1, m.b2, m.o1, m.o2, a);
   KB_LAUNCH_CHECK(kDQ ? "sa_bwd_sm100_kernel<dq>" : "sa_bwd_sm100_kernel<dkdv>");
   return KB_OK;
 }
 
 template <int D, bool BF16>
 int launch_both(const kb_sa_bwd_params& p, int32_t c, int32_t back, cudaStream_t s) {
-  if (!(p.flags & KB_FLAG_BWD_SKIP_DQ)) {
-    const int rc = launch_pass<D, BF16, true>(p, c, back, s);
+  const bool run_dq = !(p.flags & KB_FLAG_BWD_SKIP_DQ), run_dkdv = !(p.flags & KB_FLAG_BWD_SKIP_DKDV);
+  PassMaps m_dq, m_dkdv;
+  if ((run_dq && !make_pass_maps<D, true>(&m_dq, p)) || (run_dkdv && !make_pass_maps<D, false>(&m_dkdv, p)))
+    return KB_ERR_UNSUPPORTED;
+  if (run_dq) {
+    const int rc = launch_pass<D, BF16, true>(p, m_dq, c, back, s);
     if (rc) return rc;
   }
-  if (!(p.flags & KB_FLAG_BWD_SKIP_DKDV)) {
-    const int rc = launch_pass<D, BF16, false>(p, c, back, s);
+  if (run_dkdv) {
+    const int rc = launch_pass<D, BF16, false>(p, m_dkdv, c, back, s);
     if (rc) return rc;
   }
   return KB_OK;
@@ -616,8 +630,8 @@ namespace kb {
 int sa_bwd_sm100(const kb_sa_bwd_params& p, int32_t c, int32_t back, cudaStream_t s) {
   for (void* out : {p.dq, p.dk, p.dv})
     if (reinterpret_cast<uintptr_t>(out) % 16) return KB_ERR_UNSUPPORTED;
-  // tensor maps are built before anything is launched, so "unsupported" never leaves a
-  // half-finished backward behind
+  // launch_both makes the tensor maps of both passes before it launches either, so "unsupported"
+  // never leaves a half-finished backward behind
   const bool bf16 = p.dtype == KB_BF16;
   if (p.D == 64) return bf16 ? launch_both<64, true>(p, c, back, s) : launch_both<64, false>(p, c, back, s);
   if (p.D == 128) return bf16 ? launch_both<128, true>(p, c, back, s) : launch_both<128, false>(p, c, back, s);

@@ -38,6 +38,7 @@
 #include "common.cuh"
 #include "sm100_ptx.cuh"
 #include "sm100_host.h"
+#include "tiles.h"
 
 namespace kb {
 #ifdef KB_TRACE_FWD
@@ -52,10 +53,11 @@ namespace {
 
 using namespace sm100;
 
-constexpr int kBM = 128;  // rows of one q tile
-constexpr int kQTiles = 2;
-constexpr int kBN = 128;
-constexpr int kStagesK = 2, kStagesV = 2;
+constexpr int kBM = tiles::kFwdQRows;  // rows of one q tile
+constexpr int kQTiles = tiles::kFwdQTiles;
+constexpr int kBN = tiles::kFwdKeys;
+constexpr int kStagesK = tiles::kFwdStagesK, kStagesV = tiles::kFwdStagesV;
+static_assert(kBM == 128 && kBN == 128 && kQTiles == 2, "the TMEM column map and the warp roles assume two 128 x 128 score blocks");
 constexpr int kThreads = (kQTiles * 4 + 2) * 32;
 constexpr int kProducerWarp = kQTiles * 4, kMmaWarp = kQTiles * 4 + 1;
 constexpr uint32_t kTmemCols = 512;
@@ -533,7 +535,10 @@ int launch(const kb_sa_fwd_params& p, int32_t c, int32_t back, cudaStream_t s) {
   auto kern = sa_fwd_sm100_kernel<D, BF16, PACKED>;
   constexpr size_t smem = sizeof(FwdSmem<D>);
   static_assert(sizeof(FwdSmem<D>) <= 232448, "forward shared memory exceeds the 227 KB a CTA may have");
-  KB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  int dev = 0, n_sm = 0;
+  if (!device_sm_count(&dev, &n_sm)) return KB_ERR_LAUNCH;
+  static std::atomic<bool> smem_opted_in[kMaxDevices];
+  KB_CUDA_TRY(opt_in_smem_once(kern, smem, dev, smem_opted_in));
   FwdArgs a;
   a.o = p.o;
   a.lse = p.lse;
@@ -562,9 +567,6 @@ int launch(const kb_sa_fwd_params& p, int32_t c, int32_t back, cudaStream_t s) {
   a.status = p.status;
   const int64_t n_items = (int64_t)p.B * p.H * kb_cdiv_i32(Tq, kBM * kQTiles);
   if (n_items > (int64_t)1 << 30) return KB_ERR_TOO_LARGE;
-  int dev = 0, n_sm = 0;
-  KB_CUDA_TRY(cudaGetDevice(&dev));
-  KB_CUDA_TRY(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev));
   const unsigned grid = (unsigned)(n_items < n_sm ? n_items : n_sm);  // persistent: one CTA per SM
   kern<<<grid, kThreads, smem, s>>>(tm_q, tm_k, tm_v, tm_o, a);
   KB_LAUNCH_CHECK("sa_fwd_sm100_kernel");

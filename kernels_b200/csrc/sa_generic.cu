@@ -16,6 +16,8 @@
 #include <math.h>
 
 #include "common.cuh"
+#include "sm100_host.h"
+#include "tiles.h"
 
 namespace kb {
 namespace {
@@ -444,11 +446,14 @@ __global__ void __launch_bounds__(kThreads) sa_bwd_dkdv_generic_kernel(BwdArgs<T
 // ------------------------------------------------------------------------------------------
 template <int D, typename T>
 int launch_fwd(const kb_sa_fwd_params& p, int32_t c, int32_t back, cudaStream_t s) {
-  constexpr int BM = (D <= 128) ? 64 : 32, BN = BM;
+  constexpr int BM = tiles::generic_tile(D), BN = BM;
   constexpr int LD = D + kPad;
   constexpr size_t smem = sizeof(float) * (size_t)(BM * LD + 2 * BN * LD + BM * (BN + 1));
   auto kern = sa_fwd_generic_kernel<D, BM, BN, T>;
-  KB_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  int dev = 0, n_sm = 0;
+  if (!device_sm_count(&dev, &n_sm)) return KB_ERR_LAUNCH;
+  static std::atomic<bool> smem_opted_in[kMaxDevices];
+  KB_CUDA_TRY(opt_in_smem_once(kern, smem, dev, smem_opted_in));
   FwdArgs<T> a;
   a.q = make_arg<T>(p.q);
   a.k = make_arg<T>(p.k);
@@ -470,14 +475,17 @@ int launch_fwd(const kb_sa_fwd_params& p, int32_t c, int32_t back, cudaStream_t 
 
 template <int D, typename T>
 int launch_bwd(const kb_sa_bwd_params& p, int32_t c, int32_t back, cudaStream_t s) {
-  constexpr int BM = (D <= 128) ? 64 : 32, BN = BM;
+  constexpr int BM = tiles::generic_tile(D), BN = BM;
   constexpr int LD = D + kPad;
   constexpr size_t smem_dq = sizeof(float) * (size_t)(2 * BM * LD + 2 * BN * LD + BM * (BN + 1));
   constexpr size_t smem_dkdv = sizeof(float) * (size_t)(2 * BM * LD + 2 * BN * LD + 2 * BM * (BN + 1) + 2 * BM);
   auto kern_dq = sa_bwd_dq_generic_kernel<D, BM, BN, T>;
   auto kern_dkdv = sa_bwd_dkdv_generic_kernel<D, BM, BN, T>;
-  KB_CUDA_TRY(cudaFuncSetAttribute(kern_dq, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_dq));
-  KB_CUDA_TRY(cudaFuncSetAttribute(kern_dkdv, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_dkdv));
+  int dev = 0, n_sm = 0;
+  if (!device_sm_count(&dev, &n_sm)) return KB_ERR_LAUNCH;
+  static std::atomic<bool> dq_opted_in[kMaxDevices], dkdv_opted_in[kMaxDevices];
+  KB_CUDA_TRY(opt_in_smem_once(kern_dq, smem_dq, dev, dq_opted_in));
+  KB_CUDA_TRY(opt_in_smem_once(kern_dkdv, smem_dkdv, dev, dkdv_opted_in));
   BwdArgs<T> a;
   a.q = make_arg<T>(p.q);
   a.k = make_arg<T>(p.k);

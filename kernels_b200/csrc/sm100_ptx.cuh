@@ -26,16 +26,6 @@ __device__ __forceinline__ uint64_t globaltimer_ns() {
   return t;
 }
 
-__device__ __forceinline__ bool elect_one() {
-  uint32_t pred;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t.reg .b32 r;\n\t"
-      "elect.sync r|p, 0xffffffff;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(pred));
-  return pred != 0;
-}
-
 // ---- mbarrier ----------------------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
@@ -85,16 +75,18 @@ static __device__ __noinline__ bool mbar_give_up(volatile int* abort_flag, int32
   return false;
 }
 
-// kSleepNs > 0: sleep that long between polls (for roles far off the critical chain).
-template <uint32_t kSleepNs = 0>
+// kSleepNs > 0: sleep that long between polls (for roles far off the critical chain).  kLimit: polls after
+// which the wait gives up (a multiple of 64; the kernels use the default, the library's self-test a short one).
+template <uint32_t kSleepNs = 0, uint32_t kLimit = kWaitLimitSpins>
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const WaitCtx& ctx, int where) {
+  static_assert(kLimit >= 64 && kLimit % 64 == 0, "the limit is tested every 64 polls");
   if (mbar_try_wait(bar, parity)) return true;
   for (uint32_t spins = 1;; ++spins) {
     if (kSleepNs) __nanosleep(kSleepNs);
     if (mbar_try_wait(bar, parity)) return true;
     if ((spins & 63u) == 0) {
       if (*ctx.abort_flag) return false;
-      if (spins >= kWaitLimitSpins) return mbar_give_up(ctx.abort_flag, ctx.status, where);
+      if (spins >= kLimit) return mbar_give_up(ctx.abort_flag, ctx.status, where);
     }
   }
 }
@@ -133,14 +125,6 @@ __device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bu
 __device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 // at most one bulk group of this thread may still be reading its shared-memory source
 __device__ __forceinline__ void tma_store_wait_read_1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
-// Bulk fp32 reduction (performed in L2) of `bytes` contiguous bytes of shared memory into global
-// memory; both addresses 16-byte aligned, `bytes` a multiple of 16.  Completion is tracked by the
-// issuing thread's bulk groups like a tensor store.
-__device__ __forceinline__ void bulk_reduce_add_f32(float* gmem_dst, const void* smem_src, uint32_t bytes) {
-  asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.f32 [%0], [%1], %2;" ::"l"(gmem_dst),
-               "r"(smem_u32(smem_src)), "r"(bytes)
-               : "memory");
-}
 // Plain bulk copies of `bytes` contiguous bytes (a multiple of 16, both addresses 16-byte aligned):
 // shared -> global, tracked by the issuing thread's bulk groups like a tensor store ...
 __device__ __forceinline__ void bulk_store(void* gmem_dst, const void* smem_src, uint32_t bytes) {
@@ -201,16 +185,6 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
         "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
         "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
         "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr)
-      : "memory");
-}
-// 16 consecutive columns (for code that has few registers to spare)
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
       : "r"(taddr)
       : "memory");
 }
@@ -325,11 +299,6 @@ __device__ __forceinline__ void setmaxnreg_inc() {
 template <int N>
 __device__ __forceinline__ void setmaxnreg_dec() {
   asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
-}
-
-// ---- fp32 reduction into global memory (no return value, performed in L2) ----------------
-__device__ __forceinline__ void red_add_f32x4(float* addr, float a, float b, float c, float d) {
-  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
 }
 
 // ---- small math helpers ------------------------------------------------------------------

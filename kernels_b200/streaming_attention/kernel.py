@@ -30,11 +30,36 @@ _SUPPORTED_HEAD_DIMS = (16, 32, 64, 128, 256)
 _MAX_DS_SCRATCH_BYTES = 48 << 30
 
 
-def _free_bytes(device) -> int:
-    """Device memory a new allocation can draw on: free in the driver plus cached by torch."""
-    free, _total = torch.cuda.mem_get_info(device)
-    return free + torch.cuda.memory_reserved(device) - torch.cuda.memory_allocated(device)
+_device_total_bytes: dict = {}
+_ds_scratch: dict = {}
 
+
+def _ds_scratch_for(device: torch.device, stream_ptr: int, nbytes: int):
+    """The dS scratch of the single-evaluation backward: one buffer per (device, stream), kept between
+    calls and grown when a larger problem arrives, or ``None`` when the problem's scratch is withheld.
+
+    Whether to provide it is decided from sizes alone (no query of the driver on the hot path): at most
+    ``_MAX_DS_SCRATCH_BYTES`` and at most a quarter of the device's total memory.  Calls on one stream run
+    one after the other, so they can share a buffer; calls on different streams get their own.
+    """
+    if nbytes <= 0:
+        return None
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    total = _device_total_bytes.get(idx)
+    if total is None:
+        total = _device_total_bytes[idx] = torch.cuda.get_device_properties(idx).total_memory
+    if nbytes > _MAX_DS_SCRATCH_BYTES or nbytes > total // 4:
+        return None
+    key = (idx, stream_ptr)
+    buf = _ds_scratch.get(key)
+    if buf is None or buf.numel() < nbytes:
+        _ds_scratch[key] = None  # let go of the smaller one first
+        try:
+            buf = torch.empty(nbytes, dtype=torch.uint8, device=device)
+        except torch.OutOfMemoryError:
+            return None  # the two-pass kernels need no such scratch
+        _ds_scratch[key] = buf
+    return buf
 
 
 def _flags(prescale_qk: bool, precision: str) -> int:
@@ -161,9 +186,9 @@ def attention_backward_adapter(
     Scratch is allocated here and handed to the library: ``delta = rowsum(O * dO)`` as
     ``[B, H, T]`` fp32 (reference: kernel.py:1380) and, for the tcgen05 backward that evaluates
     the scores once, room for the 16-bit dS tiles (``kb_sa_bwd_workspace_bytes``; it grows with
-    ``(back_contexts + 1) * context_size``).  When that room exceeds ``_MAX_DS_SCRATCH_BYTES`` or
-    a quarter of the device memory that is free, it is withheld and the library runs its two-pass
-    kernels, which need none.  ``do`` may arrive in another dtype or with any strides
+    ``(back_contexts + 1) * context_size``; one buffer per device and stream, kept between calls).
+    When that room exceeds ``_MAX_DS_SCRATCH_BYTES`` or a quarter of the device's memory, it is
+    withheld and the library runs its two-pass kernels, which need none.  ``do`` may arrive in another dtype or with any strides
     (``tests/test_streaming_attention.py:98-112``): it is cast to
     ``q``'s dtype first.
     """
@@ -193,8 +218,7 @@ def attention_backward_adapter(
     if q.numel():
         ws_bytes = int(lib.kb_sa_bwd_workspace_bytes(
             B, H, T, D, _lib.dtype_code(q.dtype), _clamp_i32(context_size), _clamp_i32(back_contexts)))
-        if 0 < ws_bytes <= _MAX_DS_SCRATCH_BYTES and ws_bytes <= _free_bytes(q.device) // 4:
-            ds_ws = torch.empty(ws_bytes, dtype=torch.uint8, device=q.device)
+        ds_ws = _ds_scratch_for(q.device, torch.cuda.current_stream(q.device).cuda_stream, ws_bytes)
     lens_keep, lens_ptr, lens_stride = _lens_arg(lens, q.device)
     p = _lib.SaBwdParams()
     p.q, p.k, p.v, p.o, p.d_o = (_lib.tensor4(t) for t in (q, k, v, o, do))

@@ -24,7 +24,13 @@ from typing import Optional
 import torch
 
 from .. import _lib
-from .kernel import _clamp_i32, _free_bytes
+from .kernel import _clamp_i32
+
+
+def _free_bytes(device) -> int:
+    """Device memory a new allocation can draw on: free in the driver plus cached by torch."""
+    free, _total = torch.cuda.mem_get_info(device)
+    return free + torch.cuda.memory_reserved(device) - torch.cuda.memory_allocated(device)
 
 
 def _check(q, k, v, cu_seqlens, context_size, back_contexts):

@@ -84,18 +84,43 @@ def test_argument_validation_without_a_gpu():
         _lib.check(2, "x")
 
 
+def _tile_constants():
+    """The constants the kernels are compiled with (csrc/tiles.h), read from the source."""
+    import re
+
+    text = open(os.path.join(ROOT, "kernels_b200", "csrc", "tiles.h")).read()
+    return {m.group(1): int(m.group(2)) for m in re.finditer(r"\b(k[A-Za-z]+)\s*=\s*(\d+)", text)}
+
+
 def test_tile_table():
+    """kb_sa_tile_config reports exactly the constants the kernels are compiled with."""
+    k = _tile_constants()
     for dt in (torch.float16, torch.bfloat16):
         for D in (64, 128):
-            cfg = _lib.tile_config(dt, D, 256, which=0)
-            assert cfg["tile_q"] % 16 == 0 and cfg["tile_k"] % 16 == 0 and cfg["stages"] >= 1
-            for which in (1, 2, 3, 4):  # both backward families are tcgen05 kernels on 128 x 128 tiles
-                cfg = _lib.tile_config(dt, D, 256, which=which)
-                assert cfg["path"] == _lib.KB_PATH_SM100 and (cfg["tile_q"], cfg["tile_k"]) == (128, 128)
-    cfg = _lib.tile_config(torch.float32, 128, 256)
-    assert cfg["path"] == _lib.KB_PATH_GENERIC
+            for c in (64, 128, 256, 10000):
+                want = {
+                    0: (k["kFwdQRows"] * k["kFwdQTiles"], k["kFwdKeys"], k["kFwdStagesK"]),
+                    1: (k["kTwoPassStationary"], k["kTwoPassStreamed"], k["kTwoPassStagesFirst"]),
+                    2: (k["kTwoPassStreamed"], k["kTwoPassStationary"], k["kTwoPassStagesFirst"]),
+                    3: (k["kMainQueries"], k["kMainKeys"], k["kMainStagesQ"]),
+                    4: (k["kDqQueries"], k["kDqKeys"], k["kDqStages"]),
+                }
+                for which, (tq, tk, st) in want.items():
+                    cfg = _lib.tile_config(dt, D, c, which=which)
+                    assert cfg == dict(path=_lib.KB_PATH_SM100, tile_q=tq, tile_k=tk, stages=st), (dt, D, c, which, cfg)
+    # the values this build commits (a change of the table shows up here as well as in tiles.h)
+    assert _lib.tile_config(torch.bfloat16, 128, 256, which=0) == dict(path=1, tile_q=256, tile_k=128, stages=2)
+    assert _lib.tile_config(torch.bfloat16, 128, 256, which=3) == dict(path=1, tile_q=128, tile_k=128, stages=2)
+    assert _lib.tile_config(torch.bfloat16, 128, 256, which=4) == dict(path=1, tile_q=128, tile_k=128, stages=3)
+    for D, tile in ((16, 64), (128, 64), (256, 32)):
+        cfg = _lib.tile_config(torch.float32, D, 256)
+        assert cfg == dict(path=_lib.KB_PATH_GENERIC, tile_q=tile, tile_k=tile, stages=1)
     cfg = _lib.tile_config(torch.float16, 64, 256, flags=_lib.KB_FLAG_FORCE_GENERIC)
     assert cfg["path"] == _lib.KB_PATH_GENERIC
+    cfg = _lib.tile_config(torch.float16, 64, 256, unit_inner_stride=False)
+    assert cfg["path"] == _lib.KB_PATH_GENERIC
+    with pytest.raises(RuntimeError, match="bad argument"):
+        _lib.tile_config(torch.float16, 64, 0)
 
 
 def test_missing_library_fails_loudly(monkeypatch):

@@ -1,4 +1,5 @@
-"""GPU parity at the benchmark's full sizes (BASELINE.json configs 2, 3 and the shape of config 5).
+"""GPU parity at the benchmark's full sizes (the fp16 D=64 configuration, the long-sequence bf16
+configuration and the per-sequence shape of the multi-GPU configuration).
 
 The dense fp32 oracle cannot hold a T x T score matrix for every (batch, head) slice at these
 sizes, so each configuration is checked two ways:

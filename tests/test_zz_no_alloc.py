@@ -86,3 +86,27 @@ def test_noalloc_backward_rejects_problems_beyond_the_fixed_array():
     with pytest.raises(RuntimeError, match="too large"):
         _lib.check(rc, "kb_sa_bwd_noalloc")
     assert lib.kb_sa_bwd_noalloc(None, None) == 1
+
+
+def test_noalloc_backward_refuses_what_the_shared_array_cannot_serve():
+    """Partial backwards (the per-kernel timing flags) would read an earlier call's delta out of the
+    shared array; shared key/value heads and strided gradients are not served by its kernels."""
+    lib = _lib.load()
+    dev = torch.device("cuda", 0)
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    B, H, T, D = 1, 2, 256, 64
+    q, k, v, do = (torch.randn(B, H, T, D, device=dev).half() for _ in range(4))
+    o, lse = _forward(q, k, v, None, 32, 1)
+    outs = [torch.full_like(q, float("nan")) for _ in range(3)]
+    for flag in (_lib.KB_FLAG_BWD_SKIP_DQ, _lib.KB_FLAG_BWD_SKIP_DKDV, _lib.KB_FLAG_BWD_SKIP_DELTA):
+        p = _params(q, k, v, o, do, lse, *outs, None, None, 32, 1)
+        p.flags = flag
+        assert lib.kb_sa_bwd_noalloc(ctypes.byref(p), stream) == 1
+    p = _params(q, k, v, o, do, lse, *outs, None, None, 32, 1)
+    p.H_kv = 1
+    assert lib.kb_sa_bwd_noalloc(ctypes.byref(p), stream) == _lib.KB_ERR_UNSUPPORTED
+    p = _params(q, k, v, o, do, lse, *outs, None, None, 32, 1)
+    p.dq_stride[0], p.dq_stride[1], p.dq_stride[2] = H * T * D, T * D, D
+    assert lib.kb_sa_bwd_noalloc(ctypes.byref(p), stream) == _lib.KB_ERR_UNSUPPORTED
+    torch.cuda.synchronize()
+    assert all(torch.isnan(t).all() for t in outs), "a refused call must not have launched anything"
