@@ -108,11 +108,13 @@ def _run_case(B, H, T, D, c, back, dtype, lens_mode, noncontiguous, seed=20, che
         assert torch.isfinite(gc).all(), name
         torch.testing.assert_close(gc, r.to(dtype).float(), atol=atol_b, rtol=0, msg=lambda m: f"{name}\n{m}")
         assert (gc * (~res_mask)).abs().max() == 0, name
-        if dtype != torch.float32 and float(r.norm()) > 0:
+        if dtype != torch.float32:
             # the benchmark contract's bound for 16-bit kernels against the fp32 reference: relative L2 <= 2e-2
-            # (an absolute bound alone would pass a scaled-down gradient on small-magnitude cases)
-            rel = float((gc - r).norm() / r.norm())
-            assert rel <= 2e-2, f"{name}: relative L2 {rel:.3e}"
+            # (an absolute bound alone would pass a scaled-down gradient on small-magnitude cases).  The floor of
+            # 1e-4 RMS covers gradients that are zero in exact arithmetic (a query that sees a single key sends
+            # nothing to dK and dQ; the reference then holds rounding noise of the order of 1e-8).
+            err, ref_norm = float((gc - r).norm()), float(r.norm())
+            assert err <= 2e-2 * ref_norm + 1e-4 * r.numel() ** 0.5, f"{name}: relative L2 {err / max(ref_norm, 1e-30):.3e}"
 
     # base-2 LSE on valid rows
     lse_ref = SO.lse_base2_dense(q.float(), k.float(), c, back, lens)
