@@ -17,8 +17,9 @@ Prints ONE JSON line on rank 0:
                 timed on this machine's host cores on a bounded sample of the same workload.
 
 ``--impl reference`` times that CPU path alone (rank 0 only) and prints the same line shape.
-``--impl context`` (one GPU) times library kernels on the same inputs for context: compiled
-``flex_attention`` with the streaming block mask and torch SDPA with the dense mask.
+``--impl context`` (one GPU) times other implementations on the same GPU and inputs for context: the
+reference's own Triton kernel (from ``oracle/_ref``, in a child process), compiled ``flex_attention`` with
+the streaming block mask and torch SDPA with the dense mask.
 ``--workload step`` times the streaming inference step, ``--workload cfg4`` dense self-attention and softmax.
 
 Multi-GPU: launched by ``torch.distributed.run`` with one rank per GPU.  The batch x heads
@@ -440,6 +441,9 @@ def run_own(args, w):
                 "both_gbs_per_direction": copy_rate(True, True)}
     tensor_bytes = q.numel() * q.element_size()
     _lib.check_device_status()
+    config5 = None
+    if args.workload == "cfg3" and not args.no_config5:
+        config5 = _config5_block(lib, dev, rank, world)
 
     if rank == 0:
         peaks = _peaks()
@@ -481,12 +485,104 @@ def run_own(args, w):
             "gpu_launches": launches,
             "clocks": clk.summary(),
         }
+        if config5 is not None:
+            line["config5"] = config5
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"], _ = _cpu_baseline(w, steps=6, warmup=1, budget_s=25.0)
         print(json.dumps(line))
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+
+
+def _config5_block(lib, dev, rank, world, steps=5, warmup=3):
+    """The multi-GPU configuration as a STRONG-scaling record beside the headline: bf16 B=64 H=32 T=8192 D=128
+    context=64 back=8 lens~U[4096,8192], one fixed problem whose batch x heads slices ``sharding.partition``
+    spreads over the ranks (no collective).  Forward + backward through the C ABI (``kb_sa_fwd``, one
+    ``kb_sa_bwd``), device-resident, CUDA events, max over ranks.  With more than one rank, rank 0 then runs
+    the WHOLE problem alone (the other GPUs idle) so that the record carries its own t_1 and the efficiency
+    t_1 / (N t_N).  Inputs are seeded per (batch, head) slice on the device (the same slice gets the same
+    values whatever the GPU count)."""
+    import torch.distributed as dist
+
+    from kernels_b200 import _lib
+    from kernels_b200.sharding import partition, useful_pairs
+
+    w = WORKLOADS["cfg5"]
+    B, H, T, D, c, back = w["B"], w["H"], w["T"], w["D"], w["c"], w["back"]
+    dtype = TORCH_DTYPES[w["dtype"]]
+    _, lens = _global_problem(w, 1)
+    lens_list = [min(int(x), T) for x in lens.tolist()]
+    lens_d = lens.to(dev)
+    shards = partition(B, H, world, lens_list, T=T, context_size=c, back_contexts=back)
+    pairs_per_head = sum(useful_pairs(L, c, back) for L in lens_list)
+    stream = torch.cuda.current_stream(dev)
+
+    def timed(heads):
+        nh = len(heads)
+        gen = torch.Generator(device=dev)
+        q, k, v, do = (torch.empty((B, nh, T, D), dtype=dtype, device=dev) for _ in range(4))
+        rows = torch.arange(T, device=dev)[:, None]
+        for b in range(B):
+            for j, h in enumerate(heads):
+                gen.manual_seed(1_000_003 * 5 + b * H + h)
+                for dst in (q, k, v):
+                    dst[b, j].copy_(torch.randn(T, D, device=dev, generator=gen))
+                do[b, j].copy_(torch.randn(T, D, device=dev, generator=gen) * (rows < lens_list[b]))
+        o, dq, dk, dv = (torch.empty_like(q) for _ in range(4))
+        lse = torch.empty((B, nh, T), dtype=torch.float32, device=dev)
+        delta = torch.empty_like(lse)
+        ws = int(lib.kb_sa_bwd_workspace_bytes(B, nh, T, D, _lib.dtype_code(dtype), c, back))
+        ds_ws = torch.empty(ws, dtype=torch.uint8, device=dev)
+        fp = _lib.SaFwdParams()
+        fp.q, fp.k, fp.v = _lib.tensor4(q), _lib.tensor4(k), _lib.tensor4(v)
+        fp.o, fp.lse = o.data_ptr(), lse.data_ptr()
+        fp.lens, fp.lens_stride = lens_d.data_ptr(), lens_d.stride(0)
+        fp.B, fp.H, fp.T, fp.D = q.shape
+        fp.dtype = _lib.dtype_code(dtype)
+        fp.context_size, fp.back_contexts, fp.sm_scale, fp.flags = c, back, float(D ** -0.5), 0
+        fp.status = _lib.status_words().data_ptr()
+        bp = _bwd_params(_lib, q, k, v, o, do, lse, dq, dk, dv, delta, lens_d, w, 0, ds_ws)
+
+        def step():
+            _lib.check(lib.kb_sa_fwd(ctypes.byref(fp), stream.cuda_stream), "config5 forward")
+            _lib.check(lib.kb_sa_bwd(ctypes.byref(bp), stream.cuda_stream), "config5 backward")
+
+        for _ in range(warmup):
+            step()
+        torch.cuda.synchronize(dev)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(steps):
+            step()
+        e1.record(stream)
+        torch.cuda.synchronize(dev)
+        _lib.check_device_status()
+        return e0.elapsed_time(e1) / steps
+
+    shard = shards[rank]
+    assert shard.mode == "heads", "H = 32 is divisible by 1, 2, 4 and 8 GPUs"
+    if world > 1:
+        dist.barrier()
+    ms = timed(list(shard.heads))
+    t = torch.tensor([ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_n = float(t.item())
+    flops = 14.0 * D * H * pairs_per_head
+    block = {"workload": w["desc"], "scaling": "strong", "n_gpus": world, "ms_per_step": ms_n,
+             "tflops": flops / ms_n / 1e9, "useful_flops_per_step": flops, "steps": steps, "warmup": warmup,
+             "heads_per_gpu": len(shard.heads),
+             "work_spread_max_over_mean": 1.0,  # heads round-robin: every rank holds every batch entry's lens
+             "sharding": f"heads round-robin over {world} GPU(s), every rank sees all {B} lengths"}
+    if world > 1:
+        torch.cuda.empty_cache()
+        ms_1 = timed(list(range(H))) if rank == 0 else 0.0
+        dist.barrier()
+        block["ms_per_step_one_gpu_same_run"] = ms_1
+        block["strong_scaling_efficiency"] = ms_1 / (world * ms_n) if rank == 0 else None
+    torch.cuda.empty_cache()
+    return block
 
 
 def run_dense(args):
@@ -589,13 +685,77 @@ def run_step(args):
     print(json.dumps(line))
 
 
+REF_SRC = os.path.join(ROOT, "oracle", "_ref", "src")
+
+
+def run_reference_triton_child(args, w):
+    """Child process of ``--impl context``: the reference's own ``streaming_attention`` (its Triton kernels,
+    ``autotune=False``: tiles of at most 64 x 64, src/streaming_attention/kernel.py:1143-1153, 1195-1211)
+    on this GPU and the own arm's seeded inputs, forward + backward.  Runs in a process of its own because
+    the reference registers operators under the names this package uses; it imports nothing of
+    ``kernels_b200`` but the input recipe and the FLOP count."""
+    sys.path.insert(0, REF_SRC)
+    from streaming_attention import streaming_attention as ref_streaming_attention  # the reference's package
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    dtype = TORCH_DTYPES[w["dtype"]]
+    H, T, D, c, back = w["H"], w["T"], w["D"], w["c"], w["back"]
+    B, lens = _global_problem(w, 1)
+    hq, hk, hv, hdo = _make_local_inputs(w, B, list(range(H)), H, dtype, pin=False)
+    q, k, v, do = (t.to(dev) for t in (hq, hk, hv, hdo))
+    lens_d = None if lens is None else lens.to(dev)
+    pairs_total, _ = _useful_pairs_total(w, B, lens, H)
+    flops = 14.0 * D * pairs_total
+    steps, warm = max(1, min(args.steps, 10)), 3
+
+    def fwd_bwd():
+        qg, kg, vg = (t.detach().requires_grad_() for t in (q, k, v))
+        ref_streaming_attention(qg, kg, vg, lens_d, c, back, autotune=False).backward(do)
+
+    for _ in range(warm):
+        fwd_bwd()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fwd_bwd()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    import triton
+
+    print(json.dumps({"ms_per_step": ms, "tflops": flops / ms / 1e9, "autotune": False, "steps": steps,
+                      "triton": triton.__version__, "tile": f"{min(64, max(32, 1 << (c - 1).bit_length()))} x same"}))
+
+
+def _reference_triton(args):
+    """Run the child above; returns its record or why there is none."""
+    import subprocess
+
+    if not os.path.isfile(os.path.join(REF_SRC, "streaming_attention", "kernel.py")):
+        return {"unavailable": "oracle/_ref is not staged (python oracle/make_ref.py <reference checkout>)"}
+    cmd = [sys.executable, os.path.abspath(__file__), "--impl", "reference-triton", "--workload", args.workload,
+           "--steps", str(args.steps)]
+    try:
+        res = subprocess.run(cmd, capture_output=True, text=True, timeout=900)
+    except subprocess.TimeoutExpired:
+        return {"unavailable": "the reference's Triton kernels did not finish within 900 s"}
+    lines = [ln for ln in res.stdout.strip().splitlines() if ln.startswith("{")]
+    if res.returncode != 0 or not lines:
+        tail = (res.stderr.strip().splitlines() or ["no output"])[-1]
+        return {"unavailable": f"child exited {res.returncode}: {tail[:300]}"}
+    return json.loads(lines[-1])
+
+
 def run_context(args, w):
     """Context, not an arm of the comparison: library kernels on the SAME GPU and the SAME inputs as the
     own arm (the reference's benchmark times these beside its kernel,
     benchmark/benchmark_streaming_attention.py:173-243): ``flex_attention`` compiled with the streaming mask
     as a block mask, and torch SDPA with the dense boolean mask where T x T fits.  Forward + backward,
-    useful TFLOP/s by the own arm's formula.  The reference's own Triton kernel cannot run on the
-    benchmark machine (its sources do not travel)."""
+    useful TFLOP/s by the own arm's formula.  The reference's own Triton kernel is timed first, in a
+    child process (``run_reference_triton_child``)."""
+    ref_triton = _reference_triton(args)
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
     dtype = TORCH_DTYPES[w["dtype"]]
@@ -625,7 +785,7 @@ def run_context(args, w):
         qg, kg, vg = (t.detach().requires_grad_() for t in (q, k, v))
         attn(qg, kg, vg).backward(do)
 
-    out = {}
+    out = {"reference_triton": ref_triton}
     try:
         from torch.nn.attention.flex_attention import create_block_mask, flex_attention
 
@@ -665,9 +825,11 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--workload", default="cfg3", choices=sorted(WORKLOADS) + ["cfg4", "step"])
-    ap.add_argument("--impl", default="own", choices=["own", "reference", "context"])
+    ap.add_argument("--impl", default="own", choices=["own", "reference", "context", "reference-triton"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
+    ap.add_argument("--no-config5", action="store_true",
+                    help="skip the strong-scaling record of the multi-GPU configuration (profiling runs)")
     ap.add_argument("--two-pass", action="store_true",
                     help="time the two-pass backward (dQ pass + dK/dV pass) instead of the single-evaluation kernels")
     args = ap.parse_args()
@@ -678,6 +840,8 @@ def main():
     w = WORKLOADS[args.workload]
     if args.impl == "context":
         return run_context(args, w)
+    if args.impl == "reference-triton":
+        return run_reference_triton_child(args, w)
     if args.impl == "reference":
         run_reference(args, w)
     else:

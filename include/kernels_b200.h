@@ -164,6 +164,14 @@ typedef struct kb_sa_bwd_params {
   int64_t dq_stride[3];
   int64_t dkv_stride[3];
   int64_t lse_stride[2];
+  /* Packed batch in ONE launch per kernel (what kb_sa_bwd_varlen calls; NULL for every other call): DEVICE
+   * pointer to B + 1 non-decreasing row offsets, as in kb_sa_fwd_params.  q, k, v, o, d_o then describe one
+   * batch entry of `total_rows` rows, dq_stride / dkv_stride / lse_stride give the h and t strides of the packed
+   * gradients and of lse ([H, total_rows]), T is the LONGEST sequence, lens must be NULL, delta_ws holds
+   * H * total_rows floats and ds_ws kb_sa_bwd_varlen_workspace_bytes() bytes.  Single-evaluation tcgen05
+   * kernels only (anything else returns KB_ERR_UNSUPPORTED with nothing launched). */
+  const int32_t* cu_seqlens;
+  int32_t total_rows;
 } kb_sa_bwd_params;
 
 KB_API int kb_sa_bwd(const kb_sa_bwd_params* p, void* stream);
@@ -205,12 +213,14 @@ KB_API int kb_sa_bwd_noalloc(const kb_sa_bwd_params* p, void* stream);
  * [B, T] batches with `lens`, kernel.py:1586-1652): the sequences lie one after the other along the token
  * axis, q / o / dq as [total, H, D], k / v / dk / dv as [total, H_kv, D], lse as [H, total]; sequence b owns
  * the rows [cu_seqlens[b], cu_seqlens[b + 1]).  No padded row is read, computed or written.  Tiles are counted
- * from every sequence's own first row, so the results equal those of the padded call row for row.  The forward
- * is one launch over all sequences when `cu_seqlens_dev` is given, else one launch per sequence over a strided
- * view (batch 1, T = its length); the backward launches its kernels per sequence.  `cu_seqlens` is read on the
- * HOST in every case.
- * tcgen05 kernels only (f16 / bf16, D 64 or 128); the backward needs `delta_ws` (H * max_len floats) and
- * `ds_ws` (kb_sa_bwd_workspace_bytes(1, H, max_len, ...) bytes), both reused from sequence to sequence.
+ * from every sequence's own first row, so the results equal those of the padded call row for row.  With
+ * `cu_seqlens_dev` (the offsets in device memory) the forward is ONE launch over all sequences and the backward
+ * one launch of each of its three kernels; without it both launch per sequence over strided views (batch 1,
+ * T = the sequence's length).  `cu_seqlens` is read on the HOST in every case.
+ * tcgen05 kernels only (f16 / bf16, D 64 or 128).  Scratch of the backward: with `cu_seqlens_dev`, `delta_ws`
+ * holds H * total floats and `ds_ws` kb_sa_bwd_varlen_workspace_bytes() bytes; without it, `delta_ws` holds
+ * H * max_len floats and `ds_ws` kb_sa_bwd_workspace_bytes(1, H, max_len, ...) bytes per lane, reused from
+ * sequence to sequence.
  */
 typedef struct kb_sa_varlen_params {
   const void* q;
@@ -233,11 +243,11 @@ typedef struct kb_sa_varlen_params {
   float sm_scale;
   uint32_t flags;
   int32_t* status;
-  /* The same offsets in DEVICE memory, or NULL.  When given, the forward is ONE launch over all sequences (the
-   * kernel reads a sequence's first row and length from it) instead of one launch per sequence (the host copy
-   * is still read, for the checks and the longest sequence).  The backward still launches per sequence. */
+  /* The same offsets in DEVICE memory, or NULL.  When given, the forward is ONE launch over all sequences and
+   * the backward one launch per kernel (the kernels read a sequence's first row and length from it) instead of
+   * launches per sequence (the host copy is still read, for the checks and the longest sequence). */
   const int32_t* cu_seqlens_dev;
-  /* Backward only.  0 or 1: the per-sequence launches follow one another on `stream`.  2 .. 8: they are spread
+  /* Backward without `cu_seqlens_dev` only.  0 or 1: the per-sequence launches follow one another on `stream`.  2 .. 8: they are spread
    * over that many streams of the library's own (made on the first such call on a device), forked from and
    * joined back into `stream`, so that short sequences, each of which fills only a few SMs, run side by side.
    * Every lane needs scratch of its own: `delta_ws` must then hold lanes * H * max_len floats and `ds_ws`
@@ -247,6 +257,12 @@ typedef struct kb_sa_varlen_params {
 
 KB_API int kb_sa_fwd_varlen(const kb_sa_varlen_params* p, void* stream);
 KB_API int kb_sa_bwd_varlen(const kb_sa_varlen_params* p, void* stream);
+
+/* Host-only: bytes of `ds_ws` the one-launch packed backward needs (kb_sa_bwd_varlen with `cu_seqlens_dev`):
+ * one 32 KB tile per (packed key tile, query-tile slot), H * (total_rows / 128 + B + 1) * W tiles with W the
+ * most query tiles a key tile of the longest sequence meets.  0 when no such kernel covers (dtype, D). */
+KB_API uint64_t kb_sa_bwd_varlen_workspace_bytes(int32_t B, int32_t H, int32_t total_rows, int32_t max_len, int32_t D,
+                                                 int32_t dtype, int32_t context_size, int32_t back_contexts);
 
 /*
  * Dense (non-causal) self-attention forward with key padding by `lens`.

@@ -25,7 +25,8 @@ KB_NOALLOC_MAX_ROWS = 1 << 21
 _DTYPES = {torch.float32: KB_F32, torch.float16: KB_F16, torch.bfloat16: KB_BF16}
 
 EXPORTS = (
-    "kb_sa_fwd", "kb_sa_bwd", "kb_sa_bwd_workspace_bytes", "kb_sa_bwd_noalloc", "kb_sa_fwd_varlen", "kb_sa_bwd_varlen", "kb_fa_fwd", "kb_softmax_fwd", "kb_sa_plan", "kb_sa_tile_config",
+    "kb_sa_fwd", "kb_sa_bwd", "kb_sa_bwd_workspace_bytes", "kb_sa_bwd_noalloc", "kb_sa_fwd_varlen", "kb_sa_bwd_varlen",
+    "kb_sa_bwd_varlen_workspace_bytes", "kb_fa_fwd", "kb_softmax_fwd", "kb_sa_plan", "kb_sa_tile_config",
     "kb_launch_count", "kb_strerror", "kb_last_cuda_error", "kb_version", "kb_selftest_wait_timeout",
 )
 
@@ -61,6 +62,7 @@ class SaBwdParams(C.Structure):
         ("ds_ws", C.c_void_p), ("ds_ws_bytes", C.c_uint64),
         ("H_kv", C.c_int32),
         ("dq_stride", C.c_int64 * 3), ("dkv_stride", C.c_int64 * 3), ("lse_stride", C.c_int64 * 2),
+        ("cu_seqlens", C.c_void_p), ("total_rows", C.c_int32),
     ]
 
 
@@ -109,6 +111,8 @@ def load() -> C.CDLL:
     lib.kb_sa_fwd_varlen.restype = lib.kb_sa_bwd_varlen.restype = C.c_int
     lib.kb_sa_bwd_workspace_bytes.argtypes = [C.c_int32] * 7
     lib.kb_sa_bwd_workspace_bytes.restype = C.c_uint64
+    lib.kb_sa_bwd_varlen_workspace_bytes.argtypes = [C.c_int32] * 8
+    lib.kb_sa_bwd_varlen_workspace_bytes.restype = C.c_uint64
     lib.kb_softmax_fwd.argtypes = [C.POINTER(SoftmaxParams), C.c_void_p]
     for f in (lib.kb_sa_fwd, lib.kb_fa_fwd, lib.kb_sa_bwd, lib.kb_softmax_fwd):
         f.restype = C.c_int

@@ -137,6 +137,7 @@ int kb_sa_bwd(const kb_sa_bwd_params* p, void* stream) {
     return KB_ERR_BAD_ARGUMENT;
   if (!kb::out_stride_ok(p->dq_stride) || !kb::out_stride_ok(p->dkv_stride) || p->lse_stride[0] < 0 || p->lse_stride[1] < 0)
     return KB_ERR_BAD_ARGUMENT;
+  if (p->cu_seqlens && (p->lens || p->total_rows < p->T || !p->ds_ws)) return KB_ERR_BAD_ARGUMENT;
   const bool strided_out = kb::any_stride(p->dq_stride) || kb::any_stride(p->dkv_stride) || kb::any_stride(p->lse_stride);
   const int32_t c = kb_clamp_context(p->context_size, p->T);
   const int32_t back = kb_clamp_back(p->back_contexts, p->T, c);
@@ -150,13 +151,13 @@ int kb_sa_bwd(const kb_sa_bwd_params* p, void* stream) {
       if (rc != KB_ERR_UNSUPPORTED) return rc;
     }
 #endif
-    // shared K/V heads and strided gradients: single-evaluation kernels only
-    if (kb::kv_heads(p) != p->H || strided_out) return KB_ERR_UNSUPPORTED;
+    // shared K/V heads, strided gradients and packed batches: single-evaluation kernels only
+    if (kb::kv_heads(p) != p->H || strided_out || p->cu_seqlens) return KB_ERR_UNSUPPORTED;
     const int rc = kb::sa_bwd_sm100(*p, c, back, s);
     if (rc != KB_ERR_UNSUPPORTED) return rc;
   }
 #endif
-  if (kb::kv_heads(p) != p->H || strided_out) return KB_ERR_UNSUPPORTED;
+  if (kb::kv_heads(p) != p->H || strided_out || p->cu_seqlens) return KB_ERR_UNSUPPORTED;
   return kb::sa_bwd_generic(*p, c, back, s);
 }
 
@@ -269,6 +270,28 @@ int kb_sa_bwd_varlen(const kb_sa_varlen_params* p, void* stream) {
   if (p->lanes > (uint32_t)kMaxLanes) return KB_ERR_BAD_ARGUMENT;
   int32_t max_len = 0;
   for (int32_t b = 0; b < p->B; ++b) max_len = kb_max_i32(max_len, p->cu_seqlens[b + 1] - p->cu_seqlens[b]);
+  if (total == 0) return KB_OK;
+  if (p->cu_seqlens_dev) {
+    // one launch per kernel: the kernels find every sequence's first row and length in the device copy
+    kb_sa_bwd_params g = {};
+    g.q = packed_view(p->q, 0, p->H, D);
+    g.k = packed_view(p->k, 0, Hk, D);
+    g.v = packed_view(p->v, 0, Hk, D);
+    g.o = packed_view(p->o, 0, p->H, D);
+    g.d_o = packed_view(p->d_o, 0, p->H, D);
+    g.lse = p->lse;
+    g.lse_stride[0] = total * p->H, g.lse_stride[1] = total;
+    g.dq = p->dq, g.dk = p->dk, g.dv = p->dv;
+    g.dq_stride[0] = total * p->H * D, g.dq_stride[1] = D, g.dq_stride[2] = (int64_t)p->H * D;
+    g.dkv_stride[0] = total * Hk * D, g.dkv_stride[1] = D, g.dkv_stride[2] = (int64_t)Hk * D;
+    g.delta_ws = p->delta_ws;
+    g.ds_ws = p->ds_ws, g.ds_ws_bytes = p->ds_ws_bytes;
+    g.B = p->B, g.H = p->H, g.T = max_len, g.D = D, g.H_kv = Hk;
+    g.dtype = p->dtype, g.context_size = p->context_size, g.back_contexts = p->back_contexts;
+    g.sm_scale = p->sm_scale, g.flags = p->flags & ~KB_FLAG_BWD_TWO_PASS, g.status = p->status;
+    g.cu_seqlens = p->cu_seqlens_dev, g.total_rows = (int32_t)total;
+    return kb_sa_bwd(&g, stream);
+  }
   int lanes = p->lanes > 1 ? (int)p->lanes : 1;
   std::unique_lock<std::mutex> lock(g_lane_mutex, std::defer_lock);
   LanePool* pool = nullptr;
@@ -332,6 +355,19 @@ uint64_t kb_sa_bwd_workspace_bytes(int32_t B, int32_t H, int32_t T, int32_t D, i
   }
 #endif
   (void)B, (void)H, (void)T, (void)D, (void)dtype, (void)context_size, (void)back_contexts;
+  return 0;
+}
+
+uint64_t kb_sa_bwd_varlen_workspace_bytes(int32_t B, int32_t H, int32_t total_rows, int32_t max_len, int32_t D,
+                                          int32_t dtype, int32_t context_size, int32_t back_contexts) {
+#ifdef KB_HAVE_SM100_BWD_FUSED
+  if (B > 0 && H > 0 && total_rows > 0 && max_len > 0 && max_len <= total_rows && context_size >= 1 && back_contexts >= 0 &&
+      kb::sm100_shape_ok(dtype, D, 0)) {
+    const int32_t c = kb_clamp_context(context_size, max_len);
+    return kb::sa_bwd_fused_workspace_bytes_packed(B, H, total_rows, max_len, c, kb_clamp_back(back_contexts, max_len, c));
+  }
+#endif
+  (void)B, (void)H, (void)total_rows, (void)max_len, (void)D, (void)dtype, (void)context_size, (void)back_contexts;
   return 0;
 }
 

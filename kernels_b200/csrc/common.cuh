@@ -63,6 +63,7 @@ int sa_fwd_sm100(const kb_sa_fwd_params& p, int32_t c, int32_t back, cudaStream_
 int sa_bwd_sm100(const kb_sa_bwd_params& p, int32_t c, int32_t back, cudaStream_t s);
 int sa_bwd_fused_sm100(const kb_sa_bwd_params& p, int32_t c, int32_t back, cudaStream_t s);
 size_t sa_bwd_fused_workspace_bytes(int32_t B, int32_t H, int32_t T, int32_t c, int32_t back);
+size_t sa_bwd_fused_workspace_bytes_packed(int32_t B, int32_t H, int32_t total, int32_t max_len, int32_t c, int32_t back);
 int softmax_rows(const kb_softmax_params& p, cudaStream_t s);
 
 }  // namespace kb

@@ -84,7 +84,7 @@ constexpr uint32_t kColS = 0, kColDP = 128, kColDV = 256, kColDK = 384;
 #ifndef KB_WARP_ARRIVE
 #define KB_WARP_ARRIVE 0
 #endif
-constexpr uint32_t kComputeArrivals = KB_WARP_ARRIVE ? 256 / 32 : 256;
+constexpr uint32_t kComputeArrivals = KB_WARP_ARRIVE ? kComputeThreads / 32 : kComputeThreads;
 __device__ __forceinline__ void compute_arrive(uint64_t* bar, int lane) {
 #if KB_WARP_ARRIVE
   __syncwarp();
@@ -112,6 +112,11 @@ struct FusedArgs {
   int64_t dq_sb, dq_sh, dq_st, dkv_sb, dkv_sh, dkv_st;  // of dq and of dk / dv (b, h, t)
   int32_t B, H, T, c, back, W;
   int32_t Hk, group;  // key/value heads and query heads per key/value head (H = Hk * group)
+  // Packed batch: sequence b owns the rows [cu[b], cu[b + 1]) of tensors with ONE batch entry (the maps' batch
+  // extent is 1, every *_sb stride is 0), T is the longest sequence, lse and delta are [H, total rows], and the
+  // dS scratch is indexed by packed key tile (ptile_id below), n_ptiles of them per head.  NULL: padded layout.
+  const int32_t* cu;
+  int32_t total, n_ptiles;
   KbFastDiv fd_tiles, fd_H, fd_Hk, fd_group, fd_c;  // division by ceil(T / 128), H, Hk, group and c
   float scale_log2, sm_scale;
   int32_t* status;
@@ -126,6 +131,10 @@ inline int32_t fused_slots(int32_t T, int32_t c, int32_t back) {
   }
   return w;
 }
+
+// Upper bound on the key tiles of a packed batch (see ptile_id): every sequence may end one tile later than
+// its rows alone would need.
+inline int32_t packed_tiles(int32_t total, int32_t B) { return total / kBK + B + 1; }
 
 template <int D>
 struct alignas(1024) FusedSmem {
@@ -154,6 +163,7 @@ constexpr int kErrSmemAlign = 71;
 // so far; barrier phases are derived from them.
 struct Item {
   int b, hk, kt, k0, len;  // hk: key/value head
+  int row0;                // first row of the sequence in the tensor maps (packed batch: cu[b]; else 0)
   KbTileRange qr;          // query tiles [begin, end) of 128 rows that send gradient to this key tile
 };
 // The tiles of an item: for every query head of the key/value head's group (hq = 0 .. group - 1), the
@@ -171,6 +181,7 @@ struct Cursor {
 
 // `prev` is the item decoded before (b = -1: none): consecutive items mostly share the batch index
 // and with it the sequence length, which saves the global load.
+template <bool PACKED>
 __device__ __forceinline__ Item decode_item(const FusedArgs& a, int item, int n_ktiles, const Item& prev) {
   Item it;
   const int bh = kb_fastdiv(item, a.fd_tiles);
@@ -178,30 +189,48 @@ __device__ __forceinline__ Item decode_item(const FusedArgs& a, int item, int n_
   it.b = kb_fastdiv(bh, a.fd_Hk);
   it.hk = bh - it.b * a.Hk;
   it.k0 = it.kt * kBK;
-  it.len = !a.lens ? a.T : (it.b == prev.b ? prev.len : kb_clamp_len(a.lens[(int64_t)it.b * a.lens_stride], a.T));
+  it.row0 = 0;
+  if (PACKED) {
+    if (it.b == prev.b) {
+      it.row0 = prev.row0;
+      it.len = prev.len;
+    } else {
+      it.row0 = a.cu[it.b];
+      it.len = kb_min_i32(a.cu[it.b + 1] - it.row0, a.T);
+    }
+  } else {
+    it.len = !a.lens ? a.T : (it.b == prev.b ? prev.len : kb_clamp_len(a.lens[(int64_t)it.b * a.lens_stride], a.T));
+  }
   it.qr = kb_bwd_q_range_fd(it.k0, kBQ, kBK, it.len, a.c, a.back, a.fd_c);
   return it;
 }
+// Packed batch: the number a key tile has among all key tiles of all sequences.  Sequence b starts at row
+// row0 and is b-th in the batch; floor(row0 / 128) + b + kt is unique per (b, kt) and below
+// floor(total / 128) + B + 1 (a sequence ends at most one tile later than its rows alone would need).
+__device__ __forceinline__ int ptile_id(int row0, int b, int kt) { return (row0 >> 7) + b + kt; }
 // first live item at or after `item` (stride gridDim.x)
+template <bool PACKED>
 __device__ __forceinline__ void seek_live(const FusedArgs& a, Cursor& c, int n_items, int n_ktiles) {
   c.valid = false;
   for (; c.item < n_items; c.item += gridDim.x) {
-    c.it = decode_item(a, c.item, n_ktiles, c.it);
+    c.it = decode_item<PACKED>(a, c.item, n_ktiles, c.it);
     if (c.it.qr.begin < c.it.qr.end) {
       c.valid = true;
       return;
     }
   }
 }
+template <bool PACKED>
 __device__ __forceinline__ Cursor cursor_first(const FusedArgs& a, int n_items, int n_ktiles) {
   Cursor c;
   c.item = blockIdx.x;
   c.n = c.g = c.t = c.tq = c.hq = 0;
   c.group = a.group;
   c.it.b = -1;
-  seek_live(a, c, n_items, n_ktiles);
+  seek_live<PACKED>(a, c, n_items, n_ktiles);
   return c;
 }
+template <bool PACKED>
 __device__ __forceinline__ void cursor_next(const FusedArgs& a, Cursor& c, int n_items, int n_ktiles) {
   ++c.g;
   ++c.t;
@@ -212,14 +241,16 @@ __device__ __forceinline__ void cursor_next(const FusedArgs& a, Cursor& c, int n
   c.t = 0;
   ++c.n;
   c.item += gridDim.x;
-  seek_live(a, c, n_items, n_ktiles);
+  seek_live<PACKED>(a, c, n_items, n_ktiles);
 }
-// `h` is the QUERY head
-__device__ __forceinline__ uint8_t* ds_slot(const FusedArgs& a, int b, int h, int kt, int n_ktiles, int slot) {
+// `h` is the QUERY head, `row0` the sequence's first row (packed batch only)
+template <bool PACKED>
+__device__ __forceinline__ uint8_t* ds_slot(const FusedArgs& a, int b, int row0, int h, int kt, int n_ktiles, int slot) {
+  if (PACKED) return a.ds_ws + (((int64_t)h * a.n_ptiles + ptile_id(row0, b, kt)) * a.W + slot) * (int64_t)kDsTileBytes;
   return a.ds_ws + ((((int64_t)b * a.H + h) * n_ktiles + kt) * a.W + slot) * (int64_t)kDsTileBytes;
 }
 
-template <int D, bool BF16>
+template <int D, bool BF16, bool PACKED>  // PACKED: one launch over a packed batch (FusedArgs::cu)
 __global__ void __launch_bounds__(kThreads, 1)
 sa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                     const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
@@ -292,7 +323,7 @@ sa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
         prefetch_tensormap(&tm_do);
       }
       bool ok = true;
-      for (Cursor c = cursor_first(a, n_items, n_ktiles); ok && c.valid; cursor_next(a, c, n_items, n_ktiles)) {
+      for (Cursor c = cursor_first<PACKED>(a, n_items, n_ktiles); ok && c.valid; cursor_next<PACKED>(a, c, n_items, n_ktiles)) {
         const int g = c.g, n = c.n;
         const int q0 = c.q0(), hq = c.head();
         if (lane == 0) {
@@ -303,12 +334,12 @@ sa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
             // next item's tiles brought into L2 a whole item ahead of their loads
             Cursor nx = c;
             nx.t = nx.tiles() - 1;
-            cursor_next(a, nx, n_items, n_ktiles);
+            cursor_next<PACKED>(a, nx, n_items, n_ktiles);
             if (nx.valid) {
 #pragma unroll
               for (int p = 0; p < kPanels; ++p) {
-                tma_prefetch_l2_4d(&tm_k, p * 64, nx.it.k0, nx.it.hk, nx.it.b);
-                tma_prefetch_l2_4d(&tm_v, p * 64, nx.it.k0, nx.it.hk, nx.it.b);
+                tma_prefetch_l2_4d(&tm_k, p * 64, nx.it.row0 + nx.it.k0, nx.it.hk, PACKED ? 0 : nx.it.b);
+                tma_prefetch_l2_4d(&tm_v, p * 64, nx.it.row0 + nx.it.k0, nx.it.hk, PACKED ? 0 : nx.it.b);
               }
             }
             const int ks = n & 1;
@@ -318,7 +349,7 @@ sa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
               mbar_expect_tx(&sm.k_full[ks], kTileBytes);
 #pragma unroll
               for (int p = 0; p < kPanels; ++p)
-                tma_load_4d(sm.k[ks] + p * kPanelBytes, &tm_k, &sm.k_full[ks], p * 64, c.it.k0, c.it.hk, c.it.b);
+                tma_load_4d(sm.k[ks] + p * kPanelBytes, &tm_k, &sm.k_full[ks], p * 64, c.it.row0 + c.it.k0, c.it.hk, PACKED ? 0 : c.it.b);
             }
           }
           if (ok && g >= 2) ok = mbar_wait<kRelaxedNs>(&sm.q_empty[g & 1], ((g >> 1) - 1) & 1, ctx, kWQEmpty);
@@ -326,7 +357,7 @@ sa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
             mbar_expect_tx(&sm.q_full[g & 1], kTileBytes);
 #pragma unroll
             for (int p = 0; p < kPanels; ++p)
-              tma_load_4d(sm.q[g & 1] + p * kPanelBytes, &tm_q, &sm.q_full[g & 1], p * 64, q0, hq, c.it.b);
+              tma_load_4d(sm.q[g & 1] + p * kPanelBytes, &tm_q, &sm.q_full[g & 1], p * 64, c.it.row0 + q0, hq, PACKED ? 0 : c.it.b);
           }
           KB_FTR(0, g, 1);
           if (ok && c.t == 0) {
@@ -335,7 +366,7 @@ sa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
               mbar_expect_tx(&sm.v_full, kTileBytes);
 #pragma unroll
               for (int p = 0; p < kPanels; ++p)
-                tma_load_4d(sm.v + p * kPanelBytes, &tm_v, &sm.v_full, p * 64, c.it.k0, c.it.hk, c.it.b);
+                tma_load_4d(sm.v + p * kPanelBytes, &tm_v, &sm.v_full, p * 64, c.it.row0 + c.it.k0, c.it.hk, PACKED ? 0 : c.it.b);
             }
           }
           if (ok && g >= 1) ok = mbar_wait<kRelaxedNs>(&sm.do_empty, (g - 1) & 1, ctx, kWDoEmpty);
@@ -343,7 +374,7 @@ sa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
             mbar_expect_tx(&sm.do_full, kTileBytes);
 #pragma unroll
             for (int p = 0; p < kPanels; ++p)
-              tma_load_4d(sm.d_o + p * kPanelBytes, &tm_do, &sm.do_full, p * 64, q0, hq, c.it.b);
+              tma_load_4d(sm.d_o + p * kPanelBytes, &tm_do, &sm.do_full, p * 64, c.it.row0 + q0, hq, PACKED ? 0 : c.it.b);
           }
           KB_FTR(0, g, 2);
         }
@@ -354,8 +385,9 @@ sa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
         if (ok && g >= 2) ok = mbar_wait<kRelaxedNs>(&sm.ds_ready[g & 1], ((g >> 1) - 1) & 1, ctx, kWStatsSlot);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
-        const float* lse_row = a.lse + (c.it.b * a.lse_sb + hq * a.lse_sh) + q0 + lane;
-        const float* delta_row = a.delta + ((int64_t)c.it.b * a.H + hq) * T + q0 + lane;
+        const float* lse_row = a.lse + (c.it.b * a.lse_sb + hq * a.lse_sh) + c.it.row0 + q0 + lane;
+        const float* delta_row = PACKED ? a.delta + (int64_t)hq * a.total + c.it.row0 + q0 + lane
+                                        : a.delta + ((int64_t)c.it.b * a.H + hq) * T + q0 + lane;
 #pragma unroll
         for (int i = 0; i < kBQ / 32; ++i) {
           const bool valid = q0 + lane + 32 * i < c.it.len;
@@ -428,7 +460,7 @@ sa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
         Item prev;
         prev.b = -1;
         for (; item < n_items; item += gridDim.x) {
-          const Item it = decode_item(a, item, n_ktiles, prev);
+          const Item it = decode_item<PACKED>(a, item, n_ktiles, prev);
           if (it.qr.begin < it.qr.end) return (it.qr.end - it.qr.begin) * a.group;
         }
         return 0;
@@ -493,9 +525,9 @@ sa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
 #endif
     } else if (warp == kSpillWarp && lane == 0) {
       // ------------------------------ dS tiles to the scratch buffer ------------------------------
-      for (Cursor c = cursor_first(a, n_items, n_ktiles); c.valid; cursor_next(a, c, n_items, n_ktiles)) {
+      for (Cursor c = cursor_first<PACKED>(a, n_items, n_ktiles); c.valid; cursor_next<PACKED>(a, c, n_items, n_ktiles)) {
         if (!mbar_wait<kRelaxedNs>(&sm.ds_ready[c.g & 1], (c.g >> 1) & 1, ctx, kWSpill)) break;
-        bulk_store(ds_slot(a, c.it.b, c.head(), c.it.kt, n_ktiles, c.tq), sm.ds, kDsTileBytes);
+        bulk_store(ds_slot<PACKED>(a, c.it.b, c.it.row0, c.head(), c.it.kt, n_ktiles, c.tq), sm.ds, kDsTileBytes);
         tma_store_commit();
         tma_store_wait_read();
         mbar_arrive(&sm.ds_free);  // the compute warps may form the next dS in the buffer
@@ -514,7 +546,7 @@ sa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
     const float scale = a.scale_log2;
     int lo = 0, hi = 0;  // live query columns of this key row: [lo, hi)
     bool ok = true;
-    for (Cursor c = cursor_first(a, n_items, n_ktiles); ok && c.valid; cursor_next(a, c, n_items, n_ktiles)) {
+    for (Cursor c = cursor_first<PACKED>(a, n_items, n_ktiles); ok && c.valid; cursor_next<PACKED>(a, c, n_items, n_ktiles)) {
       const int g = c.g;
       if (c.t == 0) {
         const int xi = c.it.k0 + row;
@@ -631,11 +663,12 @@ sa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
     Item it;
     it.b = -1;
     for (int item = blockIdx.x; ok && item < n_items; item += gridDim.x) {
-      it = decode_item(a, item, n_ktiles, it);
+      it = decode_item<PACKED>(a, item, n_ktiles, it);
       const int kr = it.k0 + row;
       if (it.qr.begin >= it.qr.end) {
-        // the whole key tile lies in the padding: its gradients are zeros (rare; plain stores)
-        if (kr < T) {
+        // the whole key tile lies in the padding: its gradients are zeros (rare; plain stores).  A packed
+        // batch has no padding rows: a tile past the sequence's end owns nothing.
+        if (!PACKED && kr < T) {
           const int64_t off = it.b * a.dkv_sb + it.hk * a.dkv_sh + kr * a.dkv_st;  // one head per key/value head
           uint4* dv_row = reinterpret_cast<uint4*>(static_cast<uint16_t*>(a.dv) + off);
           uint4* dk_row = reinterpret_cast<uint4*>(static_cast<uint16_t*>(a.dk) + off);
@@ -648,6 +681,10 @@ sa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
         continue;
       }
       uint8_t* stage = sm.k[n & 1];
+      // Packed batch, last key tile of a sequence: the rows below it belong to the next sequence, so the tile
+      // cannot leave as a box store; every thread writes its own row (one such tile per sequence and head).
+      const bool partial = PACKED && it.k0 + kBK > it.len;
+      const int64_t row_off = it.hk * a.dkv_sh + (int64_t)(it.row0 + kr) * a.dkv_st;  // used by the partial tile only
 #pragma unroll
       for (int which = 0; which < 2; ++which) {
         const float mul = which ? a.sm_scale : 1.f;
@@ -675,17 +712,24 @@ sa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
             w.z = pack16x2<BF16>(__uint_as_float(r[8 * q4 + 4]) * mul, __uint_as_float(r[8 * q4 + 5]) * mul);
             w.w = pack16x2<BF16>(__uint_as_float(r[8 * q4 + 6]) * mul, __uint_as_float(r[8 * q4 + 7]) * mul);
             const int chunk = (cc & 1) * 4 + q4;  // 16-byte chunk within the 128-byte panel row
-            *reinterpret_cast<uint4*>(prow + ((chunk ^ (row & 7)) << 4)) = w;
+            if (partial) {
+              if (kr < it.len)
+                reinterpret_cast<uint4*>(static_cast<uint16_t*>(which ? a.dk : a.dv) + row_off)[cc * 4 + q4] = w;
+            } else {
+              *reinterpret_cast<uint4*>(prow + ((chunk ^ (row & 7)) << 4)) = w;
+            }
           }
         }
         fence_proxy_async();
         named_barrier_sync(1, kEpiThreads);
         if (etid == 0) {
+          if (!partial) {
 #pragma unroll
-          for (int p = 0; p < kPanels; ++p)
-            tma_store_4d(which ? &tm_dk : &tm_dv, stage + p * kPanelBytes, p * 64, it.k0, it.hk, it.b);
-          tma_store_commit();
-          tma_store_wait_read();
+            for (int p = 0; p < kPanels; ++p)
+              tma_store_4d(which ? &tm_dk : &tm_dv, stage + p * kPanelBytes, p * 64, it.row0 + it.k0, it.hk, PACKED ? 0 : it.b);
+            tma_store_commit();
+            tma_store_wait_read();
+          }
           if (which == 1) mbar_arrive(&sm.k_free[n & 1]);  // K(n + 2) may land in the buffer
         }
         named_barrier_sync(1, kEpiThreads);  // `stage` may be overwritten
@@ -719,20 +763,30 @@ struct DeltaArgs {
   const int32_t* lens;
   int64_t lens_stride;
   int32_t H, T;
+  const int32_t* cu;  // packed batch (see FusedArgs): rows of sequence b start at cu[b], delta is [H, total]
+  int32_t total;
 };
 
 template <int D, bool BF16>
 __global__ void __launch_bounds__(256) sa_bwd_delta_kernel(const DeltaArgs a) {
   const int b = blockIdx.z, h = blockIdx.y, x0 = blockIdx.x * kBQ;
   const int T = a.T;
-  const int len = a.lens ? kb_clamp_len(a.lens[(int64_t)b * a.lens_stride], T) : T;
-  const int64_t bh = (int64_t)b * a.H + h;
+  int len = a.lens ? kb_clamp_len(a.lens[(int64_t)b * a.lens_stride], T) : T;
+  int row0 = 0;
+  if (a.cu) {
+    row0 = a.cu[b];
+    len = kb_min_i32(a.cu[b + 1] - row0, T);
+    if (x0 >= len) return;  // a packed batch has no padding rows to clear
+  }
+  // rows a CTA may write: the tensor's in the padded layout (rows past len get 0), the sequence's when packed
+  const int row_end = a.cu ? len : T;
+  float* delta_out = a.cu ? a.delta + (int64_t)h * a.total + row0 : a.delta + ((int64_t)b * a.H + h) * T;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // a group of D/8 lanes reads one row as 16-byte chunks; warp w covers rows 16 w .. 16 w + 15
   constexpr int kLanesPerRow = D / 8, kRowsPerIter = 32 / kLanesPerRow, kIters = 16 / kRowsPerIter;
   const int sub = lane / kLanesPerRow, chunk = lane % kLanesPerRow;
-  const uint16_t* o_base = a.o + b * a.o_sb + h * a.o_sh;
-  const uint16_t* g_base = a.d_o + b * a.do_sb + h * a.do_sh;
+  const uint16_t* o_base = a.o + b * a.o_sb + h * a.o_sh + (int64_t)row0 * a.o_st;
+  const uint16_t* g_base = a.d_o + b * a.do_sb + h * a.do_sh + (int64_t)row0 * a.do_st;
   uint4 ov[kIters], gv[kIters];
 #pragma unroll
   for (int it = 0; it < kIters; ++it) {
@@ -768,7 +822,7 @@ __global__ void __launch_bounds__(256) sa_bwd_delta_kernel(const DeltaArgs a) {
 #pragma unroll
     for (int off = kLanesPerRow / 2; off > 0; off >>= 1) part += __shfl_xor_sync(0xffffffffu, part, off);
     const int r = x0 + 16 * warp + it * kRowsPerIter + sub;
-    if (chunk == 0 && r < T) a.delta[bh * T + r] = part;
+    if (chunk == 0 && r < row_end) delta_out[r] = part;
   }
 }
 
@@ -794,20 +848,33 @@ struct alignas(1024) DqSmem {
 
 struct DqItem {
   int b, h, qt, len;
+  int row0;        // first row of the sequence in the tensor maps (packed batch: cu[b]; else 0)
   KbTileRange kr;  // key tiles [begin, end) the query tile visits: the forward schedule
 };
+template <bool PACKED>
 __device__ __forceinline__ DqItem decode_dq_item(const FusedArgs& a, int item, int n_qtiles, const DqItem& prev) {
   DqItem it;
   const int bh = kb_fastdiv(item, a.fd_tiles);
   it.qt = item - bh * n_qtiles;
   it.b = kb_fastdiv(bh, a.fd_H);
   it.h = bh - it.b * a.H;
-  it.len = !a.lens ? a.T : (it.b == prev.b ? prev.len : kb_clamp_len(a.lens[(int64_t)it.b * a.lens_stride], a.T));
+  it.row0 = 0;
+  if (PACKED) {
+    if (it.b == prev.b) {
+      it.row0 = prev.row0;
+      it.len = prev.len;
+    } else {
+      it.row0 = a.cu[it.b];
+      it.len = kb_min_i32(a.cu[it.b + 1] - it.row0, a.T);
+    }
+  } else {
+    it.len = !a.lens ? a.T : (it.b == prev.b ? prev.len : kb_clamp_len(a.lens[(int64_t)it.b * a.lens_stride], a.T));
+  }
   it.kr = kb_fwd_kv_range_fd(it.qt * kBQ, kBQ, kBK, it.len, a.c, a.back, a.fd_c);
   return it;
 }
 
-template <int D, bool BF16>
+template <int D, bool BF16, bool PACKED>
 __global__ void __launch_bounds__(kDqThreads, 1)
 sa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_dq, const FusedArgs a) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -854,17 +921,17 @@ sa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
       DqItem it;
       it.b = -1;
       for (int item = blockIdx.x; ok && item < n_items; item += gridDim.x) {
-        it = decode_dq_item(a, item, n_tiles_t, it);
+        it = decode_dq_item<PACKED>(a, item, n_tiles_t, it);
         for (int j = it.kr.begin; j < it.kr.end; ++j, ++u) {
           const int s = u % kDqStages;
           if (u >= kDqStages && !mbar_wait<kRelaxedNs>(&sm.empty[s], ((u / kDqStages) - 1) & 1, ctx, kWDqEmpty)) { ok = false; break; }
           // the slot this query tile has in key tile j's list: both schedules name the same pairs
           const KbTileRange qr = kb_bwd_q_range_fd(j * kBK, kBQ, kBK, it.len, a.c, a.back, a.fd_c);
           mbar_expect_tx(&sm.full[s], kDsTileBytes + kTileBytes);
-          bulk_load(sm.ds[s], ds_slot(a, it.b, it.h, j, n_tiles_t, it.qt - qr.begin), kDsTileBytes, &sm.full[s]);
+          bulk_load(sm.ds[s], ds_slot<PACKED>(a, it.b, it.row0, it.h, j, n_tiles_t, it.qt - qr.begin), kDsTileBytes, &sm.full[s]);
 #pragma unroll
           for (int p = 0; p < kPanels; ++p)
-            tma_load_4d(sm.k[s] + p * kPanelBytes, &tm_k, &sm.full[s], p * 64, j * kBK, kb_fastdiv(it.h, a.fd_group), it.b);
+            tma_load_4d(sm.k[s] + p * kPanelBytes, &tm_k, &sm.full[s], p * 64, it.row0 + j * kBK, kb_fastdiv(it.h, a.fd_group), PACKED ? 0 : it.b);
         }
       }
     }
@@ -876,7 +943,7 @@ sa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
       DqItem it;
       it.b = -1;
       for (int item = blockIdx.x; ok && item < n_items; item += gridDim.x) {
-        it = decode_dq_item(a, item, n_tiles_t, it);
+        it = decode_dq_item<PACKED>(a, item, n_tiles_t, it);
         if (it.kr.begin >= it.kr.end) continue;
         const uint32_t acc = tmem + (m & 1) * 128;
         if (m >= 2 && !mbar_wait(&sm.acc_free[m & 1], ((m >> 1) - 1) & 1, ctx, kWDqAccFree)) break;
@@ -905,17 +972,21 @@ sa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
     DqItem it;
     it.b = -1;
     for (int item = blockIdx.x; ok && item < n_items; item += gridDim.x) {
-      it = decode_dq_item(a, item, n_tiles_t, it);
+      it = decode_dq_item<PACKED>(a, item, n_tiles_t, it);
       const int qi = it.qt * kBQ + row;
       if (it.kr.begin >= it.kr.end) {
-        // the whole query tile lies in the padding: its gradient is zero (rare; plain stores)
-        if (qi < T) {
+        // the whole query tile lies in the padding: its gradient is zero (rare; plain stores); a packed batch
+        // has no padding rows
+        if (!PACKED && qi < T) {
           uint4* dq_row = reinterpret_cast<uint4*>(static_cast<uint16_t*>(a.dq) + it.b * a.dq_sb + it.h * a.dq_sh + qi * a.dq_st);
 #pragma unroll
           for (int i = 0; i < D * 2 / 16; ++i) dq_row[i] = make_uint4(0, 0, 0, 0);
         }
         continue;
       }
+      // packed batch, last query tile of a sequence: the rows below belong to the next sequence, so no box
+      // store; every thread writes its own row
+      const bool partial = PACKED && it.qt * kBQ + kBQ > it.len;
       // all four warps must take the same exit: they meet at named barriers below
       ok = named_barrier_and(1, 128, mbar_wait<kRelaxedNs>(&sm.acc_done[m & 1], (m >> 1) & 1, ctx, kWDqAccDone));
       if (!ok) break;
@@ -938,14 +1009,20 @@ sa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
           w.z = pack16x2<BF16>(__uint_as_float(r[8 * q4 + 4]) * a.sm_scale, __uint_as_float(r[8 * q4 + 5]) * a.sm_scale);
           w.w = pack16x2<BF16>(__uint_as_float(r[8 * q4 + 6]) * a.sm_scale, __uint_as_float(r[8 * q4 + 7]) * a.sm_scale);
           const int chunk = (cc & 1) * 4 + q4;
-          *reinterpret_cast<uint4*>(prow + ((chunk ^ (row & 7)) << 4)) = w;
+          if (partial) {
+            if (qi < it.len)
+              reinterpret_cast<uint4*>(static_cast<uint16_t*>(a.dq) + it.h * a.dq_sh + (int64_t)(it.row0 + qi) * a.dq_st)[cc * 4 + q4] = w;
+          } else {
+            *reinterpret_cast<uint4*>(prow + ((chunk ^ (row & 7)) << 4)) = w;
+          }
         }
       }
       fence_proxy_async();
       named_barrier_sync(1, 128);
-      if (threadIdx.x == 0) {
+      if (threadIdx.x == 0 && !partial) {
 #pragma unroll
-        for (int p = 0; p < kPanels; ++p) tma_store_4d(&tm_dq, sm.out + p * kPanelBytes, p * 64, it.qt * kBQ, it.h, it.b);
+        for (int p = 0; p < kPanels; ++p)
+          tma_store_4d(&tm_dq, sm.out + p * kPanelBytes, p * 64, it.row0 + it.qt * kBQ, it.h, PACKED ? 0 : it.b);
         tma_store_commit();
         tma_store_wait_read();
       }
@@ -963,15 +1040,17 @@ sa_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant
   }
 }
 
-template <int D, bool BF16>
+template <int D, bool BF16, bool PACKED>
 int launch_fused(const kb_sa_bwd_params& p, int32_t c, int32_t back, cudaStream_t s) {
   CUtensorMap tm_k, tm_v, tm_q, tm_do, tm_dk, tm_dv, tm_dq;
   const int32_t Hk = p.H_kv > 0 ? p.H_kv : p.H;
-  if (!make_tile_map_4d(&tm_k, p.k, p.B, Hk, p.T, D, kBK) || !make_tile_map_4d(&tm_v, p.v, p.B, Hk, p.T, D, kBK) ||
-      !make_tile_map_4d(&tm_q, p.q, p.B, p.H, p.T, D, kBQ) || !make_tile_map_4d(&tm_do, p.d_o, p.B, p.H, p.T, D, kBQ) ||
-      !make_tile_map_4d(&tm_dk, out_view(p.dk, p.dkv_stride, Hk, p.T, D), p.B, Hk, p.T, D, kBK) ||
-      !make_tile_map_4d(&tm_dv, out_view(p.dv, p.dkv_stride, Hk, p.T, D), p.B, Hk, p.T, D, kBK) ||
-      !make_tile_map_4d(&tm_dq, out_view(p.dq, p.dq_stride, p.H, p.T, D), p.B, p.H, p.T, D, kBQ))
+  // a packed batch is ONE batch entry of `total_rows` rows as far as the maps go
+  const int32_t mB = PACKED ? 1 : p.B, mT = PACKED ? p.total_rows : p.T;
+  if (!make_tile_map_4d(&tm_k, p.k, mB, Hk, mT, D, kBK) || !make_tile_map_4d(&tm_v, p.v, mB, Hk, mT, D, kBK) ||
+      !make_tile_map_4d(&tm_q, p.q, mB, p.H, mT, D, kBQ) || !make_tile_map_4d(&tm_do, p.d_o, mB, p.H, mT, D, kBQ) ||
+      !make_tile_map_4d(&tm_dk, out_view(p.dk, p.dkv_stride, Hk, mT, D), mB, Hk, mT, D, kBK) ||
+      !make_tile_map_4d(&tm_dv, out_view(p.dv, p.dkv_stride, Hk, mT, D), mB, Hk, mT, D, kBK) ||
+      !make_tile_map_4d(&tm_dq, out_view(p.dq, p.dq_stride, p.H, mT, D), mB, p.H, mT, D, kBQ))
     return KB_ERR_UNSUPPORTED;
   const int n_tiles = kb_cdiv_i32(p.T, kBQ);
   const int64_t n_items = (int64_t)p.B * p.H * n_tiles;
@@ -982,8 +1061,8 @@ int launch_fused(const kb_sa_bwd_params& p, int32_t c, int32_t back, cudaStream_
   const int64_t n_items_main = (int64_t)p.B * Hk * n_tiles;
   const unsigned grid_main = (unsigned)(n_items_main < n_sm ? n_items_main : n_sm);
 
-  auto main_kern = sa_bwd_fused_kernel<D, BF16>;
-  auto dq_kern = sa_bwd_dq_kernel<D, BF16>;
+  auto main_kern = sa_bwd_fused_kernel<D, BF16, PACKED>;
+  auto dq_kern = sa_bwd_dq_kernel<D, BF16, PACKED>;
   static_assert(sizeof(FusedSmem<D>) <= 232448 && sizeof(DqSmem<D>) <= 232448, "shared memory exceeds the 227 KB a CTA may have");
   static std::atomic<bool> main_opted_in[kMaxDevices], dq_opted_in[kMaxDevices];
   KB_CUDA_TRY(opt_in_smem_once(main_kern, sizeof(FusedSmem<D>), dev, main_opted_in));
@@ -1003,6 +1082,9 @@ int launch_fused(const kb_sa_bwd_params& p, int32_t c, int32_t back, cudaStream_
   da.lens_stride = p.lens_stride;
   da.H = p.H;
   da.T = p.T;
+  da.cu = PACKED ? p.cu_seqlens : nullptr;
+  da.total = PACKED ? p.total_rows : 0;
+  if (PACKED) da.o_sb = da.do_sb = 0;  // the sequence's first row carries the batch offset
   if (!(p.flags & KB_FLAG_BWD_SKIP_DELTA)) {
     sa_bwd_delta_kernel<D, BF16><<<dim3(n_tiles, p.H, p.B), 256, 0, s>>>(da);
     KB_LAUNCH_CHECK("sa_bwd_delta_kernel");
@@ -1011,13 +1093,17 @@ int launch_fused(const kb_sa_bwd_params& p, int32_t c, int32_t back, cudaStream_
   FusedArgs fa;
   fa.lse = p.lse;
   {
-    const kb_tensor4 qv = out_view(p.dq, p.dq_stride, p.H, p.T, D), kv = out_view(p.dk, p.dkv_stride, Hk, p.T, D);
+    const kb_tensor4 qv = out_view(p.dq, p.dq_stride, p.H, mT, D), kv = out_view(p.dk, p.dkv_stride, Hk, mT, D);
     fa.dq_sb = qv.stride[0], fa.dq_sh = qv.stride[1], fa.dq_st = qv.stride[2];
     fa.dkv_sb = kv.stride[0], fa.dkv_sh = kv.stride[1], fa.dkv_st = kv.stride[2];
     const bool lse_packed = p.lse_stride[0] == 0 && p.lse_stride[1] == 0;
-    fa.lse_sb = lse_packed ? (int64_t)p.H * p.T : p.lse_stride[0];
-    fa.lse_sh = lse_packed ? (int64_t)p.T : p.lse_stride[1];
+    fa.lse_sb = lse_packed ? (int64_t)p.H * mT : p.lse_stride[0];
+    fa.lse_sh = lse_packed ? (int64_t)mT : p.lse_stride[1];
+    if (PACKED) fa.dq_sb = fa.dkv_sb = fa.lse_sb = 0;
   }
+  fa.cu = PACKED ? p.cu_seqlens : nullptr;
+  fa.total = PACKED ? p.total_rows : 0;
+  fa.n_ptiles = PACKED ? packed_tiles(p.total_rows, p.B) : 0;
   fa.delta = p.delta_ws;
   fa.ds_ws = static_cast<uint8_t*>(p.ds_ws);
   fa.dk = p.dk;
@@ -1066,18 +1152,29 @@ namespace kb {
 size_t sa_bwd_fused_workspace_bytes(int32_t B, int32_t H, int32_t T, int32_t c, int32_t back) {
   return (size_t)B * H * kb_cdiv_i32(T, kBK) * fused_slots(T, c, back) * kDsTileBytes;
 }
+// The same for a packed batch of B sequences with `total` rows in all and `max_len` rows in the longest.
+size_t sa_bwd_fused_workspace_bytes_packed(int32_t B, int32_t H, int32_t total, int32_t max_len, int32_t c, int32_t back) {
+  return (size_t)H * packed_tiles(total, B) * fused_slots(max_len, c, back) * kDsTileBytes;
+}
 
 int sa_bwd_fused_sm100(const kb_sa_bwd_params& p, int32_t c, int32_t back, cudaStream_t s) {
   for (void* out : {p.dq, p.dk, p.dv, p.ds_ws})
     if (reinterpret_cast<uintptr_t>(out) % 16) return KB_ERR_UNSUPPORTED;
-  if (!p.ds_ws || p.ds_ws_bytes < sa_bwd_fused_workspace_bytes(p.B, p.H, p.T, c, back)) return KB_ERR_UNSUPPORTED;
+  const size_t need = p.cu_seqlens ? sa_bwd_fused_workspace_bytes_packed(p.B, p.H, p.total_rows, p.T, c, back)
+                                   : sa_bwd_fused_workspace_bytes(p.B, p.H, p.T, c, back);
+  if (!p.ds_ws || p.ds_ws_bytes < need) return KB_ERR_UNSUPPORTED;
   // the delta kernel reads o and d_o rows with 16-byte loads
   for (const kb_tensor4* t : {&p.o, &p.d_o})
     if (t->stride[3] != 1 || reinterpret_cast<uintptr_t>(t->data) % 16 || t->stride[0] % 8 || t->stride[1] % 8 || t->stride[2] % 8)
       return KB_ERR_UNSUPPORTED;
   const bool bf16 = p.dtype == KB_BF16;
-  if (p.D == 64) return bf16 ? launch_fused<64, true>(p, c, back, s) : launch_fused<64, false>(p, c, back, s);
-  if (p.D == 128) return bf16 ? launch_fused<128, true>(p, c, back, s) : launch_fused<128, false>(p, c, back, s);
+  if (p.cu_seqlens) {
+    if (p.D == 64) return bf16 ? launch_fused<64, true, true>(p, c, back, s) : launch_fused<64, false, true>(p, c, back, s);
+    if (p.D == 128) return bf16 ? launch_fused<128, true, true>(p, c, back, s) : launch_fused<128, false, true>(p, c, back, s);
+    return KB_ERR_UNSUPPORTED;
+  }
+  if (p.D == 64) return bf16 ? launch_fused<64, true, false>(p, c, back, s) : launch_fused<64, false, false>(p, c, back, s);
+  if (p.D == 128) return bf16 ? launch_fused<128, true, false>(p, c, back, s) : launch_fused<128, false, false>(p, c, back, s);
   return KB_ERR_UNSUPPORTED;
 }
 

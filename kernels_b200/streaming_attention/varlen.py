@@ -9,12 +9,13 @@ other along the token axis, ``q`` as ``[total, H, D]`` and ``k`` / ``v`` as ``[t
 row, so the result equals the padded call row for row (``tests/test_varlen_gpu.py`` checks it bit for bit).
 
 The work is done by ``kb_sa_fwd_varlen`` / ``kb_sa_bwd_varlen`` of the C-ABI library.  The forward is ONE
-launch of the tcgen05 kernel over all sequences (it reads every sequence's first row and length from a
-device copy of ``cu_seqlens``; the last, partial tile of a sequence is written row by row so that the next
-sequence's rows stay untouched); the backward launches its kernels once per sequence over a strided view of
-the packed tensors, spread over up to eight streams of the library's own ("lanes", each with its own scratch)
-so that short sequences run side by side.  Outputs are written in place.  There is no other path: dtypes,
-head dims or layouts those kernels do not take raise.
+launch of the tcgen05 kernel over all sequences and the backward one launch of each of its three kernels
+(they read every sequence's first row and length from a device copy of ``cu_seqlens``; the last, partial
+tile of a sequence is written row by row so that the next sequence's rows stay untouched; the dS scratch is
+indexed by packed key tile).  With ``single_launch=False`` both run once per sequence over strided views of
+the packed tensors instead, the backward spread over up to eight streams of the library's own ("lanes", each
+with its own scratch).  Outputs are written in place.  There is no other path: dtypes, head dims or layouts
+those kernels do not take raise.
 """
 
 import ctypes
@@ -77,7 +78,7 @@ class _StreamingAttentionVarlen(torch.autograd.Function):
         _lib.check(rc, "kb_sa_fwd_varlen")
         ctx.mark_non_differentiable(lse)
         ctx.save_for_backward(q, k, v, o, lse)
-        ctx.cu, ctx.max_len = cu, max_len
+        ctx.cu, ctx.max_len, ctx.cu_dev = cu, max_len, cu_dev
         ctx.args = (context_size, back_contexts, sm_scale)
         return o, lse
 
@@ -89,24 +90,31 @@ class _StreamingAttentionVarlen(torch.autograd.Function):
         do = do.to(q.dtype).contiguous()
         dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
         lib = _lib.load()
-        # scratch of the longest sequence, reused from sequence to sequence (the launches of a lane are
-        # stream-ordered); with more than a few sequences the launches are spread over lanes that run side by
-        # side, each with scratch of its own, as long as that stays a small part of the free memory
-        ws_bytes = int(lib.kb_sa_bwd_workspace_bytes(1, H, max(ctx.max_len, 1), D, _lib.dtype_code(q.dtype),
-                                                     _clamp_i32(context_size), _clamp_i32(back_contexts)))
-        ws_bytes = (ws_bytes + 255) // 256 * 256
         n_seq = ctx.cu.numel() - 1
-        lanes = 1
-        if n_seq >= 4:
-            lanes = min(8, n_seq // 2)
-            while lanes > 1 and lanes * ws_bytes > _free_bytes(q.device) // 8:
-                lanes -= 1
-        delta = torch.empty(lanes * H * max(ctx.max_len, 1), dtype=torch.float32, device=q.device)
+        code, c_i, b_i = _lib.dtype_code(q.dtype), _clamp_i32(context_size), _clamp_i32(back_contexts)
+        if ctx.cu_dev is not None:
+            # one launch per kernel over the whole batch: delta per packed row, dS tiles per packed key tile
+            lanes = 1
+            ws_bytes = int(lib.kb_sa_bwd_varlen_workspace_bytes(n_seq, H, total, max(ctx.max_len, 1), D, code, c_i, b_i))
+            delta = torch.empty(H * max(total, 1), dtype=torch.float32, device=q.device)
+        else:
+            # scratch of the longest sequence, reused from sequence to sequence (the launches of a lane are
+            # stream-ordered); with more than a few sequences the launches are spread over lanes that run side
+            # by side, each with scratch of its own, as long as that stays a small part of the free memory
+            ws_bytes = int(lib.kb_sa_bwd_workspace_bytes(1, H, max(ctx.max_len, 1), D, code, c_i, b_i))
+            ws_bytes = (ws_bytes + 255) // 256 * 256
+            lanes = 1
+            if n_seq >= 4:
+                lanes = min(8, n_seq // 2)
+                while lanes > 1 and lanes * ws_bytes > _free_bytes(q.device) // 8:
+                    lanes -= 1
+            delta = torch.empty(lanes * H * max(ctx.max_len, 1), dtype=torch.float32, device=q.device)
         ds_ws = torch.empty(max(lanes * ws_bytes, 256), dtype=torch.uint8, device=q.device)
         p = _params(q, k, v, ctx.cu, context_size, back_contexts, sm_scale)
         p.o, p.lse, p.d_o = o.data_ptr(), lse.data_ptr(), do.data_ptr()
         p.dq, p.dk, p.dv = dq.data_ptr(), dk.data_ptr(), dv.data_ptr()
         p.delta_ws, p.ds_ws, p.ds_ws_bytes, p.lanes = delta.data_ptr(), ds_ws.data_ptr(), lanes * ws_bytes, lanes
+        p.cu_seqlens_dev = ctx.cu_dev.data_ptr() if ctx.cu_dev is not None else None
         with torch.cuda.device(q.device):
             rc = lib.kb_sa_bwd_varlen(ctypes.byref(p), torch.cuda.current_stream(q.device).cuda_stream)
         _lib.check(rc, "kb_sa_bwd_varlen")

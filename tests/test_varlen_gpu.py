@@ -1,8 +1,8 @@
 """GPU: streaming attention over a packed batch (``cu_seqlens``), an extension of the reference's operator.
 
 The packed call must equal the padded call (``streaming_attention`` with ``lens``) row for row and bit for
-bit: both run the same tcgen05 kernels over the same tiles of every sequence, the packed one through strided
-views of the packed tensors.  The padded call in turn is pinned to the oracle by the other GPU tests; one case
+bit: both run the same tcgen05 kernels over the same tiles of every sequence, the packed one in one launch per
+kernel over the whole batch or, with ``single_launch=False``, through strided views of the packed tensors.  The padded call in turn is pinned to the oracle by the other GPU tests; one case
 here is also checked against the oracle directly, per sequence, with the benchmark contract's tolerances.
 """
 
@@ -57,8 +57,8 @@ def test_packed_equals_padded_bitwise(H, Hk, T, D, c, back, dtype, lens, single_
     n2 = _lib.launch_count()
     _lib.check_device_status()
     live = sum(1 for L in lens if L > 0)
-    # forward: one launch for the batch or one per sequence; backward: delta + main + dQ kernels per sequence
-    assert n1 - n0 == (1 if single_launch else live) and n2 - n1 == 3 * live
+    # one launch of each kernel (forward; delta, main, dQ) for the whole batch, or one per sequence
+    assert n1 - n0 == (1 if single_launch else live) and n2 - n1 == (3 if single_launch else 3 * live)
 
     assert out.shape == qs.shape and lse.shape == (H, sum(lens))
     assert torch.equal(out, _pack(out_pad.detach(), lens))
