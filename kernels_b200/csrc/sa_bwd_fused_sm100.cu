@@ -25,9 +25,11 @@
 //               of every tile.  Phase 1 turns S into P (16-bit, back into TMEM over S); phase 2
 //               turns dP into dS (16-bit, into TMEM over dP and into shared memory);
 //   warps 8-11  epilogue: end of item, dV and dK TMEM -> 16-bit -> shared memory -> TMA store;
-//   warp 12     TMA producer (one lane) and the per-tile staging of lse / delta (whole warp);
+//   warp 12     TMA producer (one lane);
 //   warp 13     MMA issuer (one lane), owner of the TMEM allocation;
-//   warp 14     one lane sends each dS tile to the scratch buffer;   warp 15 idle.
+//   warp 14     one lane sends each dS tile to the scratch buffer;
+//   warp 15     per-tile staging of lse / delta into shared memory (whole warp; a role of its own so that the
+//               latency of its global loads never holds back the producer's next TMA load).
 // MMA issue order in steady state, tile g:   dV(g)  S(g+1)  dK(g)  dP(g+1).  MMAs execute in issue
 // order, which makes the overlays in TMEM safe without extra waits (S(g+1) overwrites P(g) after
 // dV(g) has read it, dP(g+1) overwrites dS(g) after dK(g) has read it).
@@ -74,7 +76,7 @@ static_assert(kBK == 128 && kBQ == 128 && tiles::kDqQueries == kBQ && tiles::kDq
               "the TMEM column map, the dS tile layout and the buffer indexing assume 128 x 128 tiles and double buffers");
 constexpr int kThreads = 512;
 constexpr int kComputeThreads = 256, kEpiThreads = 128;
-constexpr int kEpiWarp0 = 8, kProducerWarp = 12, kMmaWarp = 13, kSpillWarp = 14;
+constexpr int kEpiWarp0 = 8, kProducerWarp = 12, kMmaWarp = 13, kSpillWarp = 14, kStatsWarp = 15;
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kRelaxedNs = 0;  // poll interval of the roles off the critical chain (no gain measured from sleeping)
 constexpr uint32_t kColS = 0, kColDP = 128, kColDV = 256, kColDK = 384;
@@ -315,7 +317,7 @@ sa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
   if (warp >= kProducerWarp) {
     setmaxnreg_dec<kRegsOther>();
     if (warp == kProducerWarp) {
-      // ------------------------------ TMA producer + lse / delta staging ------------------------------
+      // ------------------------------ TMA producer ------------------------------
       if (lane == 0) {
         prefetch_tensormap(&tm_k);
         prefetch_tensormap(&tm_v);
@@ -378,11 +380,17 @@ sa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
           }
           KB_FTR(0, g, 2);
         }
-        // lse and delta of the tile's query rows, two slots deep: slot g & 1 was last read while dS(g - 2) was
-        // formed.  The P phase of tile g needs them the moment S(g) completes and this warp gets here only
-        // after the wait for the dO buffer, so the loop is kept short: two 64-bit multiplies per element in it
-        // cost the kernel 15 % (staging first in the loop body, or before the dO load, changed nothing).
-        if (ok && g >= 2) ok = mbar_wait<kRelaxedNs>(&sm.ds_ready[g & 1], ((g >> 1) - 1) & 1, ctx, kWStatsSlot);
+      }
+    } else if (warp == kStatsWarp) {
+      // ------------------------------ lse / delta staging ------------------------------
+      // lse and delta of the tile's query rows, two slots deep: slot g & 1 was last read while dS(g - 2) was
+      // formed.  The P phase of tile g needs them the moment S(g) completes.  The loop is kept short: two 64-bit
+      // multiplies per element in it cost the kernel 15 %.
+      bool ok = true;
+      for (Cursor c = cursor_first<PACKED>(a, n_items, n_ktiles); ok && c.valid; cursor_next<PACKED>(a, c, n_items, n_ktiles)) {
+        const int g = c.g;
+        const int q0 = c.q0(), hq = c.head();
+        if (g >= 2) ok = mbar_wait<kRelaxedNs>(&sm.ds_ready[g & 1], ((g >> 1) - 1) & 1, ctx, kWStatsSlot);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         const float* lse_row = a.lse + (c.it.b * a.lse_sb + hq * a.lse_sh) + c.it.row0 + q0 + lane;
