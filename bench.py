@@ -20,7 +20,8 @@ Prints ONE JSON line on rank 0:
 ``--impl context`` (one GPU) times other implementations on the same GPU and inputs for context: the
 reference's own Triton kernel (from ``oracle/_ref``, in a child process), compiled ``flex_attention`` with
 the streaming block mask and torch SDPA with the dense mask.
-``--workload step`` times the streaming inference step, ``--workload cfg4`` dense self-attention and softmax.
+``--workload step`` times the streaming inference step, ``--workload cfg4`` dense self-attention and softmax,
+``--workload proj`` the fused QKV + RoPE and output projections.
 
 Multi-GPU: launched by ``torch.distributed.run`` with one rank per GPU.  The batch x heads
 slices are sharded over ranks (weak scaling for cfg3/cfg2: every rank gets a full copy of the
@@ -55,6 +56,9 @@ WORKLOADS = {
     # the multi-GPU configuration: fixed total problem, batch x heads split over the GPUs
     "cfg5": dict(dtype="bf16", B=64, H=32, T=8192, D=128, c=64, back=8, lens=(4096, 8192), qk_scale=1.0,
                  scaling="strong", desc="bf16 B=64 H=32 T=8192 D=128 context=64 back=8 lens~U[4096,8192] (total)"),
+    # small stand-in for cfg5 (same tiles, schedule and length distribution, 1/16 of the batch) for ncu captures
+    "prof5": dict(dtype="bf16", B=4, H=32, T=8192, D=128, c=64, back=8, lens=(4096, 8192), qk_scale=1.0, scaling="weak",
+                  desc="bf16 B=4 H=32 T=8192 D=128 context=64 back=8 lens~U[4096,8192] (profiling case)"),
     # small stand-in for cfg3 (same tiles and schedule, 1/4 of the slices) for ncu captures
     "prof": dict(dtype="bf16", B=2, H=16, T=16384, D=128, c=256, back=2, lens=None, qk_scale=1.0, scaling="weak",
                  desc="bf16 B=2 H=16 T=16384 D=128 context=256 back=2 lens=T (profiling case)"),
@@ -748,6 +752,66 @@ def _reference_triton(args):
     return json.loads(lines[-1])
 
 
+def run_proj(args):
+    """The fused projections around the operator (no counterpart in the reference's benchmarks), at the long-sequence
+    configuration's size with a model width of 4096: x [4, 16384, 4096] -> q [4, 32, 16384, 128], k, v [4, 8, 16384, 128]
+    with rotary embedding (3.3 TFLOP), and o [4, 32, 16384, 128] -> y [4, 16384, 4096] (2.2 TFLOP), bf16.  The
+    activations (537 MB) exceed L2; the weights (50 / 34 MB) stay in it.  torch.nn.functional.linear (cuBLAS) on
+    the same shapes is timed beside them as context."""
+    from kernels_b200 import _lib
+    from kernels_b200.streaming_attention import output_projection, qkv_rope_projection, rope_tables
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    peaks = _peaks()
+    B, T, E, H, Hk, D = 4, 16384, 4096, 32, 8, 128
+    g = torch.Generator(device=dev).manual_seed(0)
+    x = torch.randn(B, T, E, device=dev, generator=g).bfloat16()
+    wqkv = (torch.randn((H + 2 * Hk) * D, E, device=dev, generator=g) * E ** -0.5).bfloat16()
+    wo = (torch.randn(E, H * D, device=dev, generator=g) * (H * D) ** -0.5).bfloat16()
+    o = torch.randn(B, H, T, D, device=dev, generator=g).bfloat16()
+    cos, sin = rope_tables(T, D, device=dev)
+
+    def timed(fn):
+        for _ in range(max(args.warmup, 3)):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / args.steps
+
+    launches0 = _lib.launch_count()
+    with ClockSampler(0) as clk:
+        qkv_ms = timed(lambda: qkv_rope_projection(x, wqkv, H, Hk, D, cos, sin))
+        out_ms = timed(lambda: output_projection(o, wo))
+    launches = _lib.launch_count() - launches0
+    _lib.check_device_status()
+    lin_qkv_ms = timed(lambda: torch.nn.functional.linear(x, wqkv))
+    lin_out_ms = timed(lambda: torch.nn.functional.linear(o.transpose(1, 2).reshape(B, T, H * D), wo))
+    f_qkv, f_out = 2.0 * B * T * E * (H + 2 * Hk) * D, 2.0 * B * T * H * D * E
+    ms = qkv_ms + out_ms
+    peak = peaks["tflops_sustained"] if ms * args.steps > 500 else peaks["tflops"]
+    line = {
+        "metric": "fused QKV+RoPE and output projection TFLOP/s", "value": (f_qkv + f_out) / ms / 1e9, "unit": "TFLOP/s",
+        "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "kernels_b200",
+        "config": {"workload": "bf16 x [4,16384,4096] -> q [4,32,16384,128], k, v [4,8,16384,128] with RoPE; o -> y [4,16384,4096]",
+                   "name": "proj", "l2": "activations larger than L2 (no flush needed)"},
+        "kernel_ms": {"qkv_rope_proj": qkv_ms, "out_proj": out_ms},
+        "kernel_tflops": {"qkv_rope_proj": f_qkv / qkv_ms / 1e9, "out_proj": f_out / out_ms / 1e9},
+        "context_cublas_linear_ms": {"qkv (no RoPE, no head layout)": lin_qkv_ms, "out (incl. the transpose copy of o)": lin_out_ms},
+        "roofline": {"kernel": "proj_sm100_kernel (QKV + RoPE)", "bound": "tensor", "achieved": f_qkv / qkv_ms / 1e9,
+                     "peak": peak, "unit": "TFLOP/s", "frac": f_qkv / qkv_ms / 1e9 / peak, "peak_source": peaks["source"],
+                     "traffic": None, "algorithmic_flops_per_launch": f_qkv},
+        "gpu_launches": launches, "clocks": clk.summary(),
+    }
+    print(json.dumps(line))
+
+
 def run_context(args, w):
     """Context, not an arm of the comparison: library kernels on the SAME GPU and the SAME inputs as the
     own arm (the reference's benchmark times these beside its kernel,
@@ -824,7 +888,7 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--workload", default="cfg3", choices=sorted(WORKLOADS) + ["cfg4", "step"])
+    ap.add_argument("--workload", default="cfg3", choices=sorted(WORKLOADS) + ["cfg4", "step", "proj"])
     ap.add_argument("--impl", default="own", choices=["own", "reference", "context", "reference-triton"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
@@ -837,6 +901,8 @@ def main():
         return run_dense(args)
     if args.workload == "step":
         return run_step(args)
+    if args.workload == "proj":
+        return run_proj(args)
     w = WORKLOADS[args.workload]
     if args.impl == "context":
         return run_context(args, w)

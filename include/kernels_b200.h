@@ -122,6 +122,41 @@ typedef struct kb_sa_fwd_params {
 KB_API int kb_sa_fwd(const kb_sa_fwd_params* p, void* stream);
 
 /*
+ * Streaming attention forward on 8-bit floating-point inputs (e4m3) with per-tile scales; no counterpart in the
+ * reference, whose kernels take fp32 / fp16 / bf16 (src/streaming_attention/kernel.py:1288-1295).  Both
+ * matmuls run as tcgen05 kind::f8f6f4, which covers 32 reduction elements per instruction instead of 16.
+ *   q [B, H, T, D], k, v [B, H_kv, T, D]: e4m3 bytes with element (= byte) strides, unit stride along D, rows
+ *     16-byte aligned; D = 128;
+ *   q_scale [B, H, n], k_scale, v_scale [B, H_kv, n] with n = ceil(T / 128): the real value of an element is
+ *     byte value * scale of its tile of 128 consecutive rows; v_scale_max [B, H_kv] = the largest v_scale of
+ *     each key/value head (> 0);
+ *   o [B, H, T, D] contiguous in `out_dtype` (KB_F16 or KB_BF16), lse [B, H, T] fp32 base 2 or NULL.
+ * The result is the streaming attention of the DEQUANTISED q, k, v up to the rounding of the probabilities to
+ * e4m3 (three mantissa bits) before P V: output max-abs <= 5e-2 and relative L2 <= 4e-2 against the fp32
+ * reference on the dequantised inputs is the tolerance the tests hold it to.  Forward only.
+ */
+typedef struct kb_sa_fwd_fp8_params {
+  kb_tensor4 q, k, v;
+  const float* q_scale;
+  const float* k_scale;
+  const float* v_scale;
+  const float* v_scale_max;
+  void* o;
+  float* lse;
+  const int32_t* lens;
+  int64_t lens_stride;
+  int32_t B, H, H_kv, T, D;
+  int32_t out_dtype;
+  int32_t context_size;
+  int32_t back_contexts;
+  float sm_scale;
+  uint32_t flags;
+  int32_t* status;
+} kb_sa_fwd_fp8_params;
+
+KB_API int kb_sa_fwd_fp8(const kb_sa_fwd_fp8_params* p, void* stream);
+
+/*
  * Streaming attention backward: dQ, dK, dV from (q, k, v, o, lse, do).
  * Replaces both launches in `attention_backward_adapter`
  * (src/streaming_attention/kernel.py:1363-1442: `_streaming_attn_bwd_precompute`, lines
@@ -263,6 +298,49 @@ KB_API int kb_sa_bwd_varlen(const kb_sa_varlen_params* p, void* stream);
  * most query tiles a key tile of the longest sequence meets.  0 when no such kernel covers (dtype, D). */
 KB_API uint64_t kb_sa_bwd_varlen_workspace_bytes(int32_t B, int32_t H, int32_t total_rows, int32_t max_len, int32_t D,
                                                  int32_t dtype, int32_t context_size, int32_t back_contexts);
+
+/*
+ * The projections on either side of the attention operator (no counterpart in the reference, whose callers
+ * run torch.nn.Linear around it; the seam is its public call, src/streaming_attention/kernel.py:1599-1652,
+ * inputs q, k, v [B, H, T, D] and output O).  Hand-written tcgen05 GEMMs that write / read the attention
+ * kernels' own layout, so q, k, v and o cross HBM once:
+ *
+ * kb_qkv_rope_proj:  [q | k | v] = x w^T with rotary position embedding applied to q and k in the epilogue.
+ *   x [B, T, E] and w [(H + 2 H_kv) D, E] (rows: the H query heads, then the H_kv key heads, then the H_kv
+ *   value heads; the layout of torch.nn.Linear.weight) are contiguous 16-bit; q [B, H, T, D] and k, v
+ *   [B, H_kv, T, D] are written contiguous, ready for kb_sa_fwd (H_kv may be smaller than H).  rope_cos /
+ *   rope_sin are fp32 tables [D / 2, T] (entry [i, t] = cos / sin of position t times frequency i), or both
+ *   NULL for no rotation; element pairs are (d, d + D / 2) of a head ("rotate half").  No bias.
+ *   Needs D in {64, 128}, E a multiple of 64, and H and H_kv multiples of 256 / D (a 256-feature tile holds
+ *   whole heads of one of q, k, v); anything else returns KB_ERR_UNSUPPORTED with nothing launched.
+ *
+ * kb_out_proj:  y = concat_heads(o) w^T.  o [B, H, T, D] with element strides (unit stride along D), w
+ *   [E_out, H D] and y [B, T, E_out] contiguous; E_out a multiple of 256.
+ */
+typedef struct kb_qkv_proj_params {
+  const void* x;
+  const void* w;
+  void* q;
+  void* k;
+  void* v;
+  const float* rope_cos;
+  const float* rope_sin;
+  int32_t B, T, E, H, H_kv, D;
+  int32_t dtype;   /* KB_F16 or KB_BF16 */
+  int32_t* status; /* KB_STATUS_WORDS words, or NULL */
+} kb_qkv_proj_params;
+
+typedef struct kb_out_proj_params {
+  kb_tensor4 o;
+  const void* w;
+  void* y;
+  int32_t B, T, H, D, E_out;
+  int32_t dtype;
+  int32_t* status;
+} kb_out_proj_params;
+
+KB_API int kb_qkv_rope_proj(const kb_qkv_proj_params* p, void* stream);
+KB_API int kb_out_proj(const kb_out_proj_params* p, void* stream);
 
 /*
  * Dense (non-causal) self-attention forward with key padding by `lens`.

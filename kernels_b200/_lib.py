@@ -25,8 +25,8 @@ KB_NOALLOC_MAX_ROWS = 1 << 21
 _DTYPES = {torch.float32: KB_F32, torch.float16: KB_F16, torch.bfloat16: KB_BF16}
 
 EXPORTS = (
-    "kb_sa_fwd", "kb_sa_bwd", "kb_sa_bwd_workspace_bytes", "kb_sa_bwd_noalloc", "kb_sa_fwd_varlen", "kb_sa_bwd_varlen",
-    "kb_sa_bwd_varlen_workspace_bytes", "kb_fa_fwd", "kb_softmax_fwd", "kb_sa_plan", "kb_sa_tile_config",
+    "kb_sa_fwd", "kb_sa_fwd_fp8", "kb_sa_bwd", "kb_sa_bwd_workspace_bytes", "kb_sa_bwd_noalloc", "kb_sa_fwd_varlen", "kb_sa_bwd_varlen",
+    "kb_sa_bwd_varlen_workspace_bytes", "kb_qkv_rope_proj", "kb_out_proj", "kb_fa_fwd", "kb_softmax_fwd", "kb_sa_plan", "kb_sa_tile_config",
     "kb_launch_count", "kb_strerror", "kb_last_cuda_error", "kb_version", "kb_selftest_wait_timeout",
 )
 
@@ -47,6 +47,17 @@ class SaFwdParams(C.Structure):
         ("o_stride", C.c_int64 * 3), ("lse_stride", C.c_int64 * 2),
         ("q_start", C.c_int32),
         ("cu_seqlens", C.c_void_p), ("total_rows", C.c_int32),
+    ]
+
+
+class SaFwdFp8Params(C.Structure):
+    _fields_ = [
+        ("q", Tensor4), ("k", Tensor4), ("v", Tensor4),
+        ("q_scale", C.c_void_p), ("k_scale", C.c_void_p), ("v_scale", C.c_void_p), ("v_scale_max", C.c_void_p),
+        ("o", C.c_void_p), ("lse", C.c_void_p), ("lens", C.c_void_p), ("lens_stride", C.c_int64),
+        ("B", C.c_int32), ("H", C.c_int32), ("H_kv", C.c_int32), ("T", C.c_int32), ("D", C.c_int32),
+        ("out_dtype", C.c_int32), ("context_size", C.c_int32), ("back_contexts", C.c_int32),
+        ("sm_scale", C.c_float), ("flags", C.c_uint32), ("status", C.c_void_p),
     ]
 
 
@@ -80,6 +91,23 @@ class SaVarlenParams(C.Structure):
     ]
 
 
+class QkvProjParams(C.Structure):
+    _fields_ = [
+        ("x", C.c_void_p), ("w", C.c_void_p), ("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p),
+        ("rope_cos", C.c_void_p), ("rope_sin", C.c_void_p),
+        ("B", C.c_int32), ("T", C.c_int32), ("E", C.c_int32), ("H", C.c_int32), ("H_kv", C.c_int32), ("D", C.c_int32),
+        ("dtype", C.c_int32), ("status", C.c_void_p),
+    ]
+
+
+class OutProjParams(C.Structure):
+    _fields_ = [
+        ("o", Tensor4), ("w", C.c_void_p), ("y", C.c_void_p),
+        ("B", C.c_int32), ("T", C.c_int32), ("H", C.c_int32), ("D", C.c_int32), ("E_out", C.c_int32),
+        ("dtype", C.c_int32), ("status", C.c_void_p),
+    ]
+
+
 class SoftmaxParams(C.Structure):
     _fields_ = [
         ("x", C.c_void_p), ("y", C.c_void_p), ("rows", C.c_int64), ("cols", C.c_int64),
@@ -104,6 +132,8 @@ def load() -> C.CDLL:
     lib.kb_sa_fwd.argtypes = [C.POINTER(SaFwdParams), C.c_void_p]
     lib.kb_fa_fwd.argtypes = [C.POINTER(SaFwdParams), C.c_void_p]
     lib.kb_sa_bwd.argtypes = [C.POINTER(SaBwdParams), C.c_void_p]
+    lib.kb_sa_fwd_fp8.argtypes = [C.POINTER(SaFwdFp8Params), C.c_void_p]
+    lib.kb_sa_fwd_fp8.restype = C.c_int
     lib.kb_sa_bwd_noalloc.argtypes = [C.POINTER(SaBwdParams), C.c_void_p]
     lib.kb_sa_bwd_noalloc.restype = C.c_int
     lib.kb_sa_fwd_varlen.argtypes = [C.POINTER(SaVarlenParams), C.c_void_p]
@@ -114,6 +144,9 @@ def load() -> C.CDLL:
     lib.kb_sa_bwd_varlen_workspace_bytes.argtypes = [C.c_int32] * 8
     lib.kb_sa_bwd_varlen_workspace_bytes.restype = C.c_uint64
     lib.kb_softmax_fwd.argtypes = [C.POINTER(SoftmaxParams), C.c_void_p]
+    lib.kb_qkv_rope_proj.argtypes = [C.POINTER(QkvProjParams), C.c_void_p]
+    lib.kb_out_proj.argtypes = [C.POINTER(OutProjParams), C.c_void_p]
+    lib.kb_qkv_rope_proj.restype = lib.kb_out_proj.restype = C.c_int
     for f in (lib.kb_sa_fwd, lib.kb_fa_fwd, lib.kb_sa_bwd, lib.kb_softmax_fwd):
         f.restype = C.c_int
     lib.kb_sa_plan.argtypes = [C.c_int32] * 6 + [C.POINTER(C.c_int32), C.POINTER(C.c_int32)]

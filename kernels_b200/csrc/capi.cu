@@ -127,6 +127,27 @@ int kb_sa_fwd(const kb_sa_fwd_params* p, void* stream) { return kb::run_fwd(p, s
 
 int kb_fa_fwd(const kb_sa_fwd_params* p, void* stream) { return kb::run_fwd(p, stream, /*dense=*/true); }
 
+int kb_sa_fwd_fp8(const kb_sa_fwd_fp8_params* p, void* stream) {
+  if (!p || p->B < 0 || p->H < 1 || p->T < 0 || p->context_size < 1 || p->back_contexts < 0) return KB_ERR_BAD_ARGUMENT;
+  const int32_t Hk = p->H_kv > 0 ? p->H_kv : p->H;
+  if (Hk > p->H || p->H % Hk) return KB_ERR_BAD_ARGUMENT;
+  if (p->D != 128 || (p->out_dtype != KB_F16 && p->out_dtype != KB_BF16)) return KB_ERR_UNSUPPORTED;
+  if (p->B > 65535 || p->H > 65535 || (int64_t)p->T > (int64_t)1 << 30) return KB_ERR_TOO_LARGE;
+  if (kb::empty(p->B, p->H, p->T)) return KB_OK;
+  if (!p->q.data || !p->k.data || !p->v.data || !p->o || !p->q_scale || !p->k_scale || !p->v_scale || !p->v_scale_max)
+    return KB_ERR_BAD_ARGUMENT;
+#ifdef KB_HAVE_SM100
+  const int32_t c = kb_clamp_context(p->context_size, p->T);
+  const int32_t back = kb_clamp_back(p->back_contexts, p->T, c);
+  kb_sa_fwd_fp8_params q = *p;
+  q.H_kv = Hk;
+  return kb::sa_fwd_sm100_fp8(q, c, back, static_cast<cudaStream_t>(stream));
+#else
+  (void)stream;
+  return KB_ERR_UNSUPPORTED;
+#endif
+}
+
 int kb_sa_bwd(const kb_sa_bwd_params* p, void* stream) {
   int rc = kb::check_common(p);
   if (rc) return rc;

@@ -60,6 +60,7 @@ struct AttnShape {
 int sa_fwd_generic(const kb_sa_fwd_params& p, int32_t c, int32_t back, cudaStream_t s);
 int sa_bwd_generic(const kb_sa_bwd_params& p, int32_t c, int32_t back, cudaStream_t s);
 int sa_fwd_sm100(const kb_sa_fwd_params& p, int32_t c, int32_t back, cudaStream_t s);
+int sa_fwd_sm100_fp8(const kb_sa_fwd_fp8_params& p, int32_t c, int32_t back, cudaStream_t s);
 int sa_bwd_sm100(const kb_sa_bwd_params& p, int32_t c, int32_t back, cudaStream_t s);
 int sa_bwd_fused_sm100(const kb_sa_bwd_params& p, int32_t c, int32_t back, cudaStream_t s);
 size_t sa_bwd_fused_workspace_bytes(int32_t B, int32_t H, int32_t T, int32_t c, int32_t back);

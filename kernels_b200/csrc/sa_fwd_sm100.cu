@@ -5,9 +5,10 @@
 // q tiles use every K/V tile that is brought into shared memory, which halves the L2 traffic
 // per FLOP against one q tile per CTA.  Ten warps, three roles (K and V rings two deep; output rows leave through shared memory and TMA stores):
 //   warps 0-3 / 4-7  softmax of q tile A / B: thread r owns query row r of its tile (= TMEM lane
-//              r).  Reads a 128 x 128 block of S from TMEM into registers, keeps the running
-//              max / sum, writes P (16-bit) back over S, rescales O when the max moved by more
-//              than 2^8, writes O / LSE at the end;
+//              r).  Walks its row of a 128 x 128 block of S in TMEM twice, 64 columns at a time (row
+//              maximum, then exponentials in packed fp32 arithmetic), keeps the running max / sum,
+//              writes P (16-bit) back over S, rescales O when the max moved by more than 2^8,
+//              writes O / LSE at the end;
 //   warp 8     TMA producer (one lane): Q once, then a ring of K tiles and a ring of V tiles;
 //   warp 9     MMA issuer (one lane): S = Q K^T (A, B from shared memory), O += P V
 //              (A = P from TMEM, B = V from shared memory, MN-major); owns the TMEM allocation.
@@ -78,6 +79,13 @@ struct FwdArgs {
   KbFastDiv fd_qblocks, fd_H, fd_c, fd_group;  // division by ceil(T / 256), H, c and H / H_kv (query heads per K/V head)
   float scale_log2;
   int32_t* status;
+  // 8-bit (e4m3) inputs only: one dequantisation scale per tile of 128 rows of q [B, H, n128], k and v
+  // [B, H_kv, n128], and the largest v scale of every key/value head [B, H_kv]
+  const float* q_scale;
+  const float* k_scale;
+  const float* v_scale;
+  const float* v_scale_max;
+  int32_t n128, Hk;
 };
 
 template <int D>
@@ -95,76 +103,110 @@ struct alignas(1024) FwdSmem {
 enum WaitSite { kWaitQ = 1, kWaitQEmpty, kWaitOFree, kWaitKEmpty, kWaitVEmpty, kWaitKFull, kWaitVFull, kWaitSReady, kWaitPReady, kWaitEpilogue };
 constexpr int kErrSmemAlign = 11;
 
-// One 128 x 128 block of scores for the thread's row: online softmax update, P into TMEM.
-// kMasked = false is the fast path for blocks in which every element of the warp's rows is live.
-// Returns the factor the O accumulator must be multiplied with (1 unless `need_rescale`).
-template <bool BF16, bool kMasked>
-__device__ __forceinline__ float softmax_block(uint32_t t_s, float scale, int k0, int lo, int hi, float& m_used, float& l,
-                                               bool& need_rescale) {
-  uint32_t s[kBN];
+// One 128 x 128 block of scores for the thread's row, in two passes over the row in TMEM, 64 columns at a
+// time, so that at most 64 scores are live in registers (holding all 128 leaves the softmax warps no register to
+// spare at the 168 the launch gives them, and every spill sits on the kernel's critical chain).
+// Pass 1 (softmax_row_max): the row maximum of the masked scores.  kMasked = false is the fast path for blocks
+// in which every element of the warp's rows is live.
+template <bool kMasked>
+__device__ __forceinline__ float softmax_row_max(uint32_t t_s, int k0, int lo, int hi) {
+  float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-  for (int cc = 0; cc < kBN / 32; ++cc) tmem_ld32(t_s + cc * 32, reinterpret_cast<uint32_t(&)[32]>(s[cc * 32]));
-  tmem_wait_ld();
-  // Masking works on 32-column groups with warp-wide votes: a group that is live for every row of the
-  // warp needs no select, one that is masked for every row needs no exponentials either (chunk
-  // boundaries that are multiples of 32 never leave a mixed group).
-  bool dead[kBN / 32] = {};
-  if (kMasked) {
+  for (int half = 0; half < 2; ++half) {
+    uint32_t s[64];
+    tmem_ld32(t_s + half * 64, reinterpret_cast<uint32_t(&)[32]>(s[0]));
+    tmem_ld32(t_s + half * 64 + 32, reinterpret_cast<uint32_t(&)[32]>(s[32]));
+    tmem_wait_ld();
 #pragma unroll
-    for (int cc = 0; cc < kBN / 32; ++cc) {
-      const int c0 = k0 + cc * 32;
-      const bool all_live = __all_sync(0xffffffffu, lo <= c0 && c0 + 32 <= hi);
-      dead[cc] = __all_sync(0xffffffffu, c0 + 32 <= lo || c0 >= hi);
-      if (!all_live) {
+    for (int cc = 0; cc < 2; ++cc) {
+      const int c0 = k0 + half * 64 + cc * 32;
+      // a 32-column group that is live for every row of the warp needs no select, one that is masked for every
+      // row contributes nothing (chunk boundaries that are multiples of 32 never leave a mixed group)
+      const bool all_live = !kMasked || __all_sync(0xffffffffu, lo <= c0 && c0 + 32 <= hi);
+      const bool all_dead = kMasked && __all_sync(0xffffffffu, c0 + 32 <= lo || c0 >= hi);
+      if (all_dead) continue;
+      // 3-input max: two scores per instruction
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int col = c0 + i;
-          s[cc * 32 + i] = (col >= lo && col < hi) ? s[cc * 32 + i] : 0xff800000u;  // -inf
+      for (int i = 0; i < 32; i += 8) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int j = cc * 32 + i + 2 * e;
+          float a = __uint_as_float(s[j]), b = __uint_as_float(s[j + 1]);
+          if (!all_live) {
+            a = (c0 + i + 2 * e >= lo && c0 + i + 2 * e < hi) ? a : -INFINITY;
+            b = (c0 + i + 2 * e + 1 >= lo && c0 + i + 2 * e + 1 < hi) ? b : -INFINITY;
+          }
+          mx[e] = fmax3(mx[e], a, b);
         }
       }
     }
   }
-  float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-  for (int i = 0; i < kBN; i += 4) {
-#pragma unroll
-    for (int e = 0; e < 4; ++e) mx[e] = fmaxf(mx[e], __uint_as_float(s[i + e]));
-  }
-  const float m_new = fmaxf(m_used, fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * scale);
-  // lazy rescale: keep the old reference maximum unless the new one is > 2^8 larger
-  need_rescale = m_new > m_used + kRescaleThreshold;
-  float alpha = 1.f;
-  if (need_rescale) {
-    alpha = ex2_approx(m_used - m_new);
-    m_used = m_new;
-    l *= alpha;
-  }
-  const float m_safe = (m_used == -INFINITY) ? 0.f : m_used;
-  float sum[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-  for (int cc = 0; cc < kBN / 32; ++cc) {
-    uint32_t pk[16];
-    if (kMasked && dead[cc]) {
-#pragma unroll
-      for (int i = 0; i < 16; ++i) pk[i] = 0u;
-      tmem_st16(t_s + cc * 16, pk);
-      continue;
-    }
-#pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      const float p0 = ex2_approx(fmaf(__uint_as_float(s[cc * 32 + 2 * i]), scale, -m_safe));
-      const float p1 = ex2_approx(fmaf(__uint_as_float(s[cc * 32 + 2 * i + 1]), scale, -m_safe));
-      sum[(2 * i) & 3] += p0;
-      sum[(2 * i + 1) & 3] += p1;
-      pk[i] = pack16x2<BF16>(p0, p1);
-    }
-    tmem_st16(t_s + cc * 16, pk);
-  }
-  l += (sum[0] + sum[1]) + (sum[2] + sum[3]);
-  return alpha;
+  return fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
 }
 
-template <int D, bool BF16, bool PACKED>  // PACKED: one launch over a packed batch (FwdArgs::cu)
+// Pass 2 (softmax_exp_half): P = 2^(S scale - m) for the 64 columns [64 half, 64 half + 64) of the row, 16-bit,
+// into TMEM over S (P of columns 32 j .. 32 j + 31 lands on columns 16 j .. 16 j + 15: the second half of P
+// overwrites only scores of the first half, which are in registers by then); the row sum goes into `sum`.
+// FP8: P is written as e4m3, four values per TMEM column (64 keys = 16 columns at 16 half), for the 8-bit P V.
+template <bool BF16, bool kMasked, bool FP8>
+__device__ __forceinline__ void softmax_exp_half(uint32_t t_s, int half, float scale, float m_used, int k0, int lo, int hi,
+                                                 float (&sum)[4]) {
+  const float m_safe = (m_used == -INFINITY) ? 0.f : m_used;
+  // packed fp32 arithmetic: one FMA and one add per PAIR of scores
+  const uint64_t scale2 = f2_pack(scale, scale), negm2 = f2_pack(-m_safe, -m_safe);
+  uint64_t sum01 = f2_pack(sum[0], sum[1]), sum23 = f2_pack(sum[2], sum[3]);
+  uint32_t s[64];
+  tmem_ld32(t_s + half * 64, reinterpret_cast<uint32_t(&)[32]>(s[0]));
+  tmem_ld32(t_s + half * 64 + 32, reinterpret_cast<uint32_t(&)[32]>(s[32]));
+  tmem_wait_ld();
+#pragma unroll
+  for (int cc = 0; cc < 2; ++cc) {
+    const int c0 = k0 + half * 64 + cc * 32;
+    const bool all_live = !kMasked || __all_sync(0xffffffffu, lo <= c0 && c0 + 32 <= hi);
+    const bool all_dead = kMasked && __all_sync(0xffffffffu, c0 + 32 <= lo || c0 >= hi);
+    uint32_t pk[16];
+    if (all_dead) {
+#pragma unroll
+      for (int i = 0; i < 16; ++i) pk[i] = 0u;
+      if (FP8) tmem_st8(t_s + (half * 2 + cc) * 8, reinterpret_cast<const uint32_t(&)[8]>(pk[0]));
+      else tmem_st16(t_s + (half * 2 + cc) * 16, pk);
+      continue;
+    }
+    float pf[FP8 ? 32 : 1];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      float s0 = __uint_as_float(s[cc * 32 + 2 * i]), s1 = __uint_as_float(s[cc * 32 + 2 * i + 1]);
+      if (!all_live) {
+        s0 = (c0 + 2 * i >= lo && c0 + 2 * i < hi) ? s0 : -INFINITY;
+        s1 = (c0 + 2 * i + 1 >= lo && c0 + 2 * i + 1 < hi) ? s1 : -INFINITY;
+      }
+      const uint64_t x = f2_fma(f2_pack(s0, s1), scale2, negm2);
+      float x0, x1;
+      f2_unpack(x, x0, x1);
+      const float p0 = ex2_approx(x0), p1 = ex2_approx(x1);
+      if (i & 1) sum23 = f2_add(sum23, f2_pack(p0, p1)); else sum01 = f2_add(sum01, f2_pack(p0, p1));
+      if (FP8) {
+        pf[2 * i] = p0;
+        pf[2 * i + 1] = p1;
+      } else {
+        pk[i] = pack16x2<BF16>(p0, p1);
+      }
+    }
+    if (FP8) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) pk[i] = pack_e4m3x4(pf[4 * i], pf[4 * i + 1], pf[4 * i + 2], pf[4 * i + 3]);
+      tmem_st8(t_s + (half * 2 + cc) * 8, reinterpret_cast<const uint32_t(&)[8]>(pk[0]));
+    } else {
+      tmem_st16(t_s + (half * 2 + cc) * 16, pk);
+    }
+  }
+  f2_unpack(sum01, sum[0], sum[1]);
+  f2_unpack(sum23, sum[2], sum[3]);
+}
+
+// PACKED: one launch over a packed batch (FwdArgs::cu).  FP8: q, k, v are e4m3 with per-tile scales, both matmuls
+// run as kind::f8f6f4 (half the instructions), the output is 16-bit (BF16 selects which).
+template <int D, bool BF16, bool PACKED, bool FP8>
 __global__ void __launch_bounds__(kThreads, 1)
 sa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                     const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o, const FwdArgs a) {
@@ -244,8 +286,10 @@ sa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   const uint32_t tmem = sm.tmem_base;
   const WaitCtx ctx{&sm.abort_flag, a.status};
   constexpr uint32_t kPanelBytes = 128 * 128;  // 128 rows x 128 bytes
-  constexpr uint32_t kTileBytes = 128 * D * 2;
-  constexpr int kPanels = D / 64;
+  constexpr uint32_t kTileBytes = 128 * D * (FP8 ? 1 : 2);
+  constexpr int kPanels = FP8 ? D / 128 : D / 64;  // 128-byte panels of an input row
+  constexpr int kPanelElems = FP8 ? 128 : 64;
+  constexpr int kOutPanels = D / 64;               // of a 16-bit output row
 
   // Barrier phases are counted over the whole life of the CTA: kc / vc = K / V tiles so far,
   // na = items with at least one live q tile so far, per q tile: tiles and items so far.
@@ -268,7 +312,7 @@ sa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
           if (!it.act[x]) continue;
 #pragma unroll
           for (int p = 0; p < kPanels; ++p)
-            tma_load_4d(sm.q[x] + p * kPanelBytes, &tm_q, &sm.q_full, p * 64, it.row0 + it.q0 - a.q_start + x * kBM, it.h, PACKED ? 0 : it.b);
+            tma_load_4d(sm.q[x] + p * kPanelBytes, &tm_q, &sm.q_full, p * kPanelElems, it.row0 + it.q0 - a.q_start + x * kBM, it.h, PACKED ? 0 : it.b);
         }
         const int h_kv = kb_fastdiv(it.h, a.fd_group);  // the K/V head this query head reads
         for (int t = it.u_begin; t < it.u_end; ++t, ++kc, ++vc) {
@@ -277,11 +321,11 @@ sa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
           if (kc >= kStagesK && !mbar_wait(&sm.k_empty[sk], ((kc / kStagesK) - 1) & 1, ctx, kWaitKEmpty)) { ok = false; break; }
           mbar_expect_tx(&sm.k_full[sk], kTileBytes);
 #pragma unroll
-          for (int p = 0; p < kPanels; ++p) tma_load_4d(sm.k[sk] + p * kPanelBytes, &tm_k, &sm.k_full[sk], p * 64, it.row0 + k0, h_kv, PACKED ? 0 : it.b);
+          for (int p = 0; p < kPanels; ++p) tma_load_4d(sm.k[sk] + p * kPanelBytes, &tm_k, &sm.k_full[sk], p * kPanelElems, it.row0 + k0, h_kv, PACKED ? 0 : it.b);
           if (vc >= kStagesV && !mbar_wait(&sm.v_empty[sv], ((vc / kStagesV) - 1) & 1, ctx, kWaitVEmpty)) { ok = false; break; }
           mbar_expect_tx(&sm.v_full[sv], kTileBytes);
 #pragma unroll
-          for (int p = 0; p < kPanels; ++p) tma_load_4d(sm.v[sv] + p * kPanelBytes, &tm_v, &sm.v_full[sv], p * 64, it.row0 + k0, h_kv, PACKED ? 0 : it.b);
+          for (int p = 0; p < kPanels; ++p) tma_load_4d(sm.v[sv] + p * kPanelBytes, &tm_v, &sm.v_full[sv], p * kPanelElems, it.row0 + k0, h_kv, PACKED ? 0 : it.b);
         }
         ++na;
       }
@@ -289,8 +333,8 @@ sa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   } else if (warp == kMmaWarp) {
     // ------------------------------ MMA issuer ------------------------------
     if (lane == 0) {
-      constexpr uint32_t idesc_qk = make_idesc(BF16, kBM, kBN, false, false);
-      constexpr uint32_t idesc_pv = make_idesc(BF16, kBM, D, false, true);
+      constexpr uint32_t idesc_qk = FP8 ? make_idesc_e4m3(kBM, kBN, false, false) : make_idesc(BF16, kBM, kBN, false, false);
+      constexpr uint32_t idesc_pv = FP8 ? make_idesc_e4m3(kBM, D, false, true) : make_idesc(BF16, kBM, D, false, true);
       int kbase = 0, na = 0;            // K (= V) tiles of earlier items, live items so far
       int tiles_x[kQTiles] = {0, 0};    // S / P blocks of q tile x so far
       int items_x[kQTiles] = {0, 0};    // items in which q tile x was live so far
@@ -327,11 +371,18 @@ sa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
               // short issue loops (four instructions per trip, descriptor low words stepped by adds): the
               // scalar work between two MMAs is what the tensor pipe waits for
               uint32_t p_col = tmem + kColS + x * 128, v_lo = desc_lo_mnmajor(smem_u32(sm.v[sv]), kPanelBytes);
-#pragma unroll 1
-              for (int h = 0; h < kBN / 64; ++h, p_col += 32, v_lo += 4 * (2048 >> 4)) {
+              if (FP8) {
+                // 128 keys = four instructions of 32 keys: 8 packed columns of P, 32 rows (4096 bytes) of V each
 #pragma unroll
                 for (int i = 0; i < 4; ++i)
-                  mma_ts_lo(tmem + kColO + x * 128, p_col + 8 * i, v_lo + i * (2048 >> 4), idesc_pv, lx > 0 || h > 0 || i > 0);
+                  mma_ts_lo_f8(tmem + kColO + x * 128, p_col + 8 * i, v_lo + i * (4096 >> 4), idesc_pv, lx > 0 || i > 0);
+              } else {
+#pragma unroll 1
+                for (int h = 0; h < kBN / 64; ++h, p_col += 32, v_lo += 4 * (2048 >> 4)) {
+#pragma unroll
+                  for (int i = 0; i < 4; ++i)
+                    mma_ts_lo(tmem + kColO + x * 128, p_col + 8 * i, v_lo + i * (2048 >> 4), idesc_pv, lx > 0 || h > 0 || i > 0);
+                }
               }
               // V_u is free once the last q tile that uses it has consumed it
               const bool last_user = (x == kQTiles - 1) || !(u >= it.kr[1].begin && u < it.kr[1].end);
@@ -347,9 +398,12 @@ sa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
               tc_fence_after();
               uint32_t q_lo = desc_lo_kmajor(smem_u32(sm.q[x])), k_lo = desc_lo_kmajor(smem_u32(sm.k[sk]));
 #pragma unroll 1
-              for (int h = 0; h < D / 64; ++h, q_lo += kPanelBytes >> 4, k_lo += kPanelBytes >> 4) {
+              for (int h = 0; h < kPanels; ++h, q_lo += kPanelBytes >> 4, k_lo += kPanelBytes >> 4) {
 #pragma unroll
-                for (int i = 0; i < 4; ++i) mma_ss_lo(tmem + kColS + x * 128, q_lo + 2 * i, k_lo + 2 * i, idesc_qk, h > 0 || i > 0);
+                for (int i = 0; i < 4; ++i) {  // 32 bytes of every row per instruction: 16 16-bit or 32 8-bit elements
+                  if (FP8) mma_ss_lo_f8(tmem + kColS + x * 128, q_lo + 2 * i, k_lo + 2 * i, idesc_qk, h > 0 || i > 0);
+                  else mma_ss_lo(tmem + kColS + x * 128, q_lo + 2 * i, k_lo + 2 * i, idesc_qk, h > 0 || i > 0);
+                }
               }
               const bool last_user = (x == kQTiles - 1) || !(t >= it.kr[1].begin && t < it.kr[1].end);
               if (last_user) mma_commit(&sm.k_empty[sk]);
@@ -376,7 +430,7 @@ sa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     const int row = (warp & 3) * 32 + lane;
     const uint32_t t_lane = tmem + ((uint32_t)((warp & 3) * 32) << 16);
     const uint32_t t_s = t_lane + kColS + x * 128, t_o = t_lane + kColO + x * 128;
-    const float scale = a.scale_log2;
+    const float scale_base = a.scale_log2;
     int tiles = 0, items = 0;  // S blocks / live items of this q tile so far
     bool ok = true;
 #ifdef KB_TRACE_FWD
@@ -408,21 +462,45 @@ sa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         hi = h64 < it.len ? (int)h64 : it.len;
       }
       float m_used = -INFINITY, l = 0.f;
+      // 8-bit inputs: the scores of a tile carry the scales of its q and k tiles (folded into the softmax scale);
+      // P of a tile is formed as p * 256 * (v scale of the tile) / (largest v scale of the head), which uses
+      // e4m3's range (<= 256) and lets one accumulator add tiles with different v scales: the factor enters
+      // the exponent (p_off) and is taken out of the tile's row sum again; O is divided by it at the end.
+      float q_sc = 1.f, v_inv_max = 1.f, v_max = 1.f;
+      const float* k_sc_row = nullptr;
+      const float* v_sc_row = nullptr;
+      if (FP8) {
+        const int h_kv = kb_fastdiv(it.h, a.fd_group);
+        q_sc = a.q_scale[((int64_t)it.b * a.H + it.h) * a.n128 + ((it.q0 + x * kBM) >> 7)];
+        k_sc_row = a.k_scale + ((int64_t)it.b * a.Hk + h_kv) * a.n128;
+        v_sc_row = a.v_scale + ((int64_t)it.b * a.Hk + h_kv) * a.n128;
+        v_max = a.v_scale_max[(int64_t)it.b * a.Hk + h_kv];
+        v_inv_max = 1.f / v_max;
+      }
 
       for (int lx = 0; lx < n_tiles; ++lx, ++tiles) {
         const int k0 = (it.kr[x].begin + lx) * kBN;
+        float scale = scale_base, p_off = 0.f;
+        if (FP8) {
+          scale = scale_base * q_sc * k_sc_row[k0 >> 7];
+          p_off = 8.f + log2f(fmaxf(v_sc_row[k0 >> 7] * v_inv_max, 9.5367431640625e-7f));  // log2(256 v / v_max)
+        }
         KB_FACC(0);
         ok = __all_sync(0xffffffffu, mbar_wait(&sm.s_ready[x], tiles & 1, ctx, kWaitSReady));
         if (!ok) break;
         tc_fence_after();
         KB_FACC(1);
         const bool warp_full = __all_sync(0xffffffffu, lo <= k0 && k0 + kBN <= hi);
-        bool need;
-        float alpha;
-        if (warp_full)
-          alpha = softmax_block<BF16, false>(t_s, scale, k0, lo, hi, m_used, l, need);
-        else
-          alpha = softmax_block<BF16, true>(t_s, scale, k0, lo, hi, m_used, l, need);
+        const float row_max = warp_full ? softmax_row_max<false>(t_s, k0, lo, hi) : softmax_row_max<true>(t_s, k0, lo, hi);
+        const float m_new = fmaxf(m_used, row_max * scale);
+        // lazy rescale: keep the old reference maximum unless the new one is > 2^8 larger
+        const bool need = m_new > m_used + kRescaleThreshold;
+        float alpha = 1.f;
+        if (need) {
+          alpha = ex2_approx(m_used - m_new);
+          m_used = m_new;
+          l *= alpha;
+        }
         KB_FACC(2);
         if (lx > 0 && __any_sync(0xffffffffu, need)) {
           // S(lx) is complete, so the P V of the previous tile (issued before it) is too: O is idle
@@ -437,9 +515,17 @@ sa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
           }
         }
         KB_FACC(3);
+        float sum[4] = {0.f, 0.f, 0.f, 0.f};
+        const float m_exp = m_used - p_off;  // 2^(s scale - m_exp) = p * 2^p_off
+        if (warp_full) softmax_exp_half<BF16, false, FP8>(t_s, 0, scale, m_exp, k0, lo, hi, sum);
+        else softmax_exp_half<BF16, true, FP8>(t_s, 0, scale, m_exp, k0, lo, hi, sum);
+        if (warp_full) softmax_exp_half<BF16, false, FP8>(t_s, 1, scale, m_exp, k0, lo, hi, sum);
+        else softmax_exp_half<BF16, true, FP8>(t_s, 1, scale, m_exp, k0, lo, hi, sum);
         tmem_wait_st();
         tc_fence_before();
         mbar_arrive(&sm.p_ready[x]);
+        if (FP8) l += ((sum[0] + sum[1]) + (sum[2] + sum[3])) * ex2_approx(-p_off);
+        else l += (sum[0] + sum[1]) + (sum[2] + sum[3]);
         KB_FACC(4);
       }
       if (!ok) break;
@@ -458,7 +544,7 @@ sa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       tc_fence_before();
       mbar_arrive(&sm.o_free[x]);
       const bool valid = qi < it.len;
-      const float inv = valid ? 1.f / l : 0.f;
+      const float inv = valid ? (FP8 ? v_max * 0.00390625f / l : 1.f / l) : 0.f;
       // The rows leave through shared memory and a TMA store, one 64-column panel at a time (row = 128
       // bytes, 128-byte swizzle).  Plain 16-byte stores of a 256-byte row per thread touch 32 different
       // lines per instruction and held the softmax warps for several thousand clocks per item.  Rows past
@@ -482,7 +568,7 @@ sa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         }
       } else {
 #pragma unroll
-      for (int p = 0; p < kPanels; ++p) {
+      for (int p = 0; p < kOutPanels; ++p) {
         if (row == 0) tma_store_wait_read();  // the store that used the buffer last has read it
         named_barrier_sync(1 + x, kBM);
 #pragma unroll
@@ -521,18 +607,22 @@ sa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
   }
 }
 
-template <int D, bool BF16, bool PACKED>
-int launch(const kb_sa_fwd_params& p, int32_t c, int32_t back, cudaStream_t s) {
+// `f8`: the scales of 8-bit inputs (FP8 only; q, k, v of `p` are then e4m3 tensors with byte strides)
+template <int D, bool BF16, bool PACKED, bool FP8>
+int launch(const kb_sa_fwd_params& p, int32_t c, int32_t back, cudaStream_t s, const kb_sa_fwd_fp8_params* f8 = nullptr) {
   CUtensorMap tm_q, tm_k, tm_v, tm_o;
   const int32_t H_kv = p.H_kv > 0 ? p.H_kv : p.H;
   const int32_t Tq = p.T - p.q_start;  // rows of q, o and lse
   // a packed batch is ONE batch entry of `total_rows` rows as far as the maps go
   const int32_t mapB = p.cu_seqlens ? 1 : p.B, mapTq = p.cu_seqlens ? p.total_rows : Tq, mapT = p.cu_seqlens ? p.total_rows : p.T;
-  if (!make_tile_map_4d(&tm_q, p.q, mapB, p.H, mapTq, D, kBM) || !make_tile_map_4d(&tm_k, p.k, mapB, H_kv, mapT, D, kBN) ||
-      !make_tile_map_4d(&tm_v, p.v, mapB, H_kv, mapT, D, kBN) ||
-      !make_tile_map_4d(&tm_o, out_view(p.o, p.o_stride, p.H, mapTq, D), mapB, p.H, mapTq, D, kBM))
+  const bool maps_ok =
+      FP8 ? make_tile_map_4d_u8(&tm_q, p.q, mapB, p.H, mapTq, D, kBM) && make_tile_map_4d_u8(&tm_k, p.k, mapB, H_kv, mapT, D, kBN) &&
+                make_tile_map_4d_u8(&tm_v, p.v, mapB, H_kv, mapT, D, kBN)
+          : make_tile_map_4d(&tm_q, p.q, mapB, p.H, mapTq, D, kBM) && make_tile_map_4d(&tm_k, p.k, mapB, H_kv, mapT, D, kBN) &&
+                make_tile_map_4d(&tm_v, p.v, mapB, H_kv, mapT, D, kBN);
+  if (!maps_ok || !make_tile_map_4d(&tm_o, out_view(p.o, p.o_stride, p.H, mapTq, D), mapB, p.H, mapTq, D, kBM))
     return KB_ERR_UNSUPPORTED;
-  auto kern = sa_fwd_sm100_kernel<D, BF16, PACKED>;
+  auto kern = sa_fwd_sm100_kernel<D, BF16, PACKED, FP8>;
   constexpr size_t smem = sizeof(FwdSmem<D>);
   static_assert(sizeof(FwdSmem<D>) <= 232448, "forward shared memory exceeds the 227 KB a CTA may have");
   int dev = 0, n_sm = 0;
@@ -565,6 +655,12 @@ int launch(const kb_sa_fwd_params& p, int32_t c, int32_t back, cudaStream_t s) {
   a.fd_group = kb_fastdiv_make(p.H / H_kv);
   a.scale_log2 = p.sm_scale * kLog2e;
   a.status = p.status;
+  a.q_scale = f8 ? f8->q_scale : nullptr;
+  a.k_scale = f8 ? f8->k_scale : nullptr;
+  a.v_scale = f8 ? f8->v_scale : nullptr;
+  a.v_scale_max = f8 ? f8->v_scale_max : nullptr;
+  a.n128 = kb_cdiv_i32(p.T, 128);
+  a.Hk = H_kv;
   const int64_t n_items = (int64_t)p.B * p.H * kb_cdiv_i32(Tq, kBM * kQTiles);
   if (n_items > (int64_t)1 << 30) return KB_ERR_TOO_LARGE;
   const unsigned grid = (unsigned)(n_items < n_sm ? n_items : n_sm);  // persistent: one CTA per SM
@@ -579,13 +675,27 @@ int sa_fwd_sm100(const kb_sa_fwd_params& p, int32_t c, int32_t back, cudaStream_
   if (!(p.sm_scale > 0.f) || reinterpret_cast<uintptr_t>(p.o) % 16) return KB_ERR_UNSUPPORTED;
   const bool bf16 = p.dtype == KB_BF16;
   if (p.cu_seqlens) {
-    if (p.D == 64) return bf16 ? launch<64, true, true>(p, c, back, s) : launch<64, false, true>(p, c, back, s);
-    if (p.D == 128) return bf16 ? launch<128, true, true>(p, c, back, s) : launch<128, false, true>(p, c, back, s);
+    if (p.D == 64) return bf16 ? launch<64, true, true, false>(p, c, back, s) : launch<64, false, true, false>(p, c, back, s);
+    if (p.D == 128) return bf16 ? launch<128, true, true, false>(p, c, back, s) : launch<128, false, true, false>(p, c, back, s);
     return KB_ERR_UNSUPPORTED;
   }
-  if (p.D == 64) return bf16 ? launch<64, true, false>(p, c, back, s) : launch<64, false, false>(p, c, back, s);
-  if (p.D == 128) return bf16 ? launch<128, true, false>(p, c, back, s) : launch<128, false, false>(p, c, back, s);
+  if (p.D == 64) return bf16 ? launch<64, true, false, false>(p, c, back, s) : launch<64, false, false, false>(p, c, back, s);
+  if (p.D == 128) return bf16 ? launch<128, true, false, false>(p, c, back, s) : launch<128, false, false, false>(p, c, back, s);
   return KB_ERR_UNSUPPORTED;
+}
+
+// 8-bit (e4m3) q, k, v with per-tile scales; head dim 128, padded layout, all query rows.
+int sa_fwd_sm100_fp8(const kb_sa_fwd_fp8_params& f, int32_t c, int32_t back, cudaStream_t s) {
+  if (!(f.sm_scale > 0.f) || reinterpret_cast<uintptr_t>(f.o) % 16 || f.D != 128) return KB_ERR_UNSUPPORTED;
+  kb_sa_fwd_params p = {};
+  p.q = f.q, p.k = f.k, p.v = f.v;
+  p.o = f.o, p.lse = f.lse;
+  p.lens = f.lens, p.lens_stride = f.lens_stride;
+  p.B = f.B, p.H = f.H, p.T = f.T, p.D = f.D, p.H_kv = f.H_kv;
+  p.dtype = f.out_dtype;
+  p.context_size = f.context_size, p.back_contexts = f.back_contexts;
+  p.sm_scale = f.sm_scale, p.flags = f.flags, p.status = f.status;
+  return f.out_dtype == KB_BF16 ? launch<128, true, false, true>(p, c, back, s, &f) : launch<128, false, false, true>(p, c, back, s, &f);
 }
 
 }  // namespace kb

@@ -126,6 +126,31 @@ inline bool encode_tile_map_4d(CUtensorMap* out, const kb_tensor4& t, int B, int
   return r == CUDA_SUCCESS;
 }
 
+// Map over an 8-bit [B, H, T, D] tensor with element (= byte) strides, D = 128: a box is [box_rows x 128] bytes of
+// one (b, h) (one 128-byte swizzled line per row); rows past T read as zeros.  Not cached (the 8-bit entry
+// point makes three per call).
+inline bool make_tile_map_4d_u8(CUtensorMap* out, const kb_tensor4& t, int B, int H, int T, int D, int box_rows) {
+  EncodeTiledFn enc = encode_tiled_fn();
+  if (!enc || D != 128) return false;
+  if (t.stride[3] != 1 || reinterpret_cast<uintptr_t>(t.data) % 16) return false;
+  const cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)T, (cuuint64_t)H, (cuuint64_t)B};
+  int64_t st[3] = {t.stride[2], t.stride[1], t.stride[0]};  // t, h, b
+  const int64_t extent[3] = {T, H, B};
+  int64_t fallback = D;
+  for (int i = 0; i < 3; ++i) {
+    if (extent[i] == 1) st[i] = fallback;
+    if (st[i] <= 0 || st[i] % 16 || st[i] >= ((int64_t)1 << 40)) return false;
+    fallback = st[i] * extent[i];
+  }
+  const cuuint64_t strides[3] = {(cuuint64_t)st[0], (cuuint64_t)st[1], (cuuint64_t)st[2]};
+  const cuuint32_t box[4] = {128, (cuuint32_t)box_rows, 1, 1};
+  const cuuint32_t elem[4] = {1, 1, 1, 1};
+  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void*>(t.data), dims, strides, box, elem,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
 // An output tensor as a strided view: `stride` holds the element strides of its b, h, t axes, all zeros
 // meaning [B, H, T, D] contiguous.
 inline kb_tensor4 out_view(void* data, const int64_t (&stride)[3], int H, int T, int D) {

@@ -10,7 +10,11 @@ the earlier rows.  With a cache of ``back + 1`` chunks and ``Tq = c`` this is th
 ``Tq`` is a chunked prefill.
 
 Forward only (inference), through ``kb_sa_fwd`` with ``q_start = T - Tq`` on the tcgen05 kernels
-(fp16 / bf16, head_dim 64 or 128); anything else raises: there is no other path.
+(fp16 / bf16, head_dim 64 or 128).  The other shapes of the operator's surface (fp32, head_dim 16, 32, 256,
+odd strides; ``kernel.py:1289``) go through the generic CUDA kernels, which compute whole sequences: the
+queries are placed at the end of a zero tensor of ``T`` rows, the whole-sequence operator runs, and the last
+``Tq`` rows are returned (correct, at the cost of the earlier rows' work; those shapes are not the
+performance path).  There is no CPU path.
 """
 
 import ctypes
@@ -67,6 +71,17 @@ def streaming_attention_step(
     p.q_start = T - Tq
     with torch.cuda.device(q.device):
         rc = _lib.load().kb_sa_fwd(ctypes.byref(p), torch.cuda.current_stream(q.device).cuda_stream)
-    _lib.check(rc, "kb_sa_fwd (streaming step)")
     del lens_keep
+    if rc == _lib.KB_ERR_UNSUPPORTED:
+        # no tcgen05 kernel for this dtype / head_dim / layout: whole-sequence call of the generic kernels
+        from .kernel import streaming_attention
+
+        with torch.no_grad():
+            q_full = torch.zeros((B, H, T, D), dtype=q.dtype, device=q.device)
+            q_full[:, :, T - Tq:] = q
+            o_full, lse_full = streaming_attention(q_full, k, v, lens, context_size, back_contexts, sm_scale=sm_scale,
+                                                   return_lse=True)
+        o, lse = o_full[:, :, T - Tq:].contiguous(), lse_full[:, :, T - Tq:].contiguous()
+        return (o, lse) if return_lse else o
+    _lib.check(rc, "kb_sa_fwd (streaming step)")
     return (o, lse) if return_lse else o

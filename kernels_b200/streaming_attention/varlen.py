@@ -15,7 +15,8 @@ tile of a sequence is written row by row so that the next sequence's rows stay u
 indexed by packed key tile).  With ``single_launch=False`` both run once per sequence over strided views of
 the packed tensors instead, the backward spread over up to eight streams of the library's own ("lanes", each
 with its own scratch).  Outputs are written in place.  There is no other path: dtypes, head dims or layouts
-those kernels do not take raise.
+those kernels do not take (fp32, head_dim 16, 32 or 256) run sequence by sequence through the padded
+operator and its generic CUDA kernels (see ``streaming_attention_varlen``).
 """
 
 import ctypes
@@ -142,5 +143,30 @@ def streaming_attention_varlen(
     """
     if sm_scale is None:
         sm_scale = 1.0 / math.sqrt(q.shape[-1])
+    if q.is_cuda and (q.dtype == torch.float32 or q.shape[-1] not in (64, 128)) and q.shape[-1] in (16, 32, 64, 128, 256):
+        return _varlen_generic(q, k, v, cu_seqlens, context_size, back_contexts, sm_scale, return_lse)
     o, lse = _StreamingAttentionVarlen.apply(q, k, v, cu_seqlens, context_size, back_contexts, sm_scale, single_launch)
     return (o, lse) if return_lse else o
+
+
+def _varlen_generic(q, k, v, cu_seqlens, context_size, back_contexts, sm_scale, return_lse):
+    """Shapes without a tcgen05 kernel (the rest of the operator's surface, ``kernel.py:1289``): every sequence
+    goes through the padded operator as a batch of one (generic CUDA kernels, autograd included), and the
+    results are concatenated.  Same rows as the packed kernels would give; not a performance path."""
+    from .kernel import streaming_attention
+
+    cu, _ = _check(q, k, v, cu_seqlens, context_size, back_contexts)
+    outs, lses = [], []
+    for b in range(cu.numel() - 1):
+        r0, r1 = int(cu[b]), int(cu[b + 1])
+        if r1 == r0:
+            continue
+        qs, ks, vs = (t[r0:r1].transpose(0, 1).unsqueeze(0) for t in (q, k, v))  # [1, heads, len, D] views
+        o, lse = streaming_attention(qs, ks, vs, None, context_size, back_contexts, sm_scale=sm_scale, return_lse=True)
+        outs.append(o[0].transpose(0, 1))
+        lses.append(lse[0])
+    if not outs:
+        o, lse = torch.empty_like(q), torch.empty((q.shape[1], 0), dtype=torch.float32, device=q.device)
+    else:
+        o, lse = torch.cat(outs, dim=0), torch.cat(lses, dim=1)
+    return (o, lse.detach()) if return_lse else o

@@ -102,12 +102,24 @@ def test_rolling_cache_reproduces_the_whole_sequence():
     _lib.check_device_status()
 
 
-def test_step_rejects_what_the_kernels_do_not_take():
+def test_step_shapes_without_a_tcgen05_kernel_use_the_generic_kernels():
+    """fp32 and head dims 16 / 32 / 256 (the rest of the operator's surface): the step equals the whole-sequence
+    call's last rows, here against the oracle with the reference's fp32 / fp16 forward tolerances."""
     from kernels_b200.streaming_attention import streaming_attention_step
 
-    q, k, v = (t.cuda() for t in _inputs(1, 2, 2, 256, 64, torch.float32))
-    with pytest.raises(RuntimeError, match="unsupported"):
-        streaming_attention_step(q[:, :, 128:], k, v, None, 64, 1)  # fp32: no tcgen05 kernel
+    for dtype, D, tol in ((torch.float32, 64, 5e-6), (torch.float16, 32, 3e-3), (torch.float32, 256, 5e-6)):
+        q, k, v = _inputs(2, 2, 2, 256, D, dtype)
+        lens = torch.tensor([256, 200], dtype=torch.int32)
+        ref, _, _ = SO.streaming_attention_oracle(q.float(), k.float(), v.float(), 64, 1, lens)
+        ref = ref * (torch.arange(256)[None] < lens[:, None])[:, None, :, None]
+        out, lse = streaming_attention_step(q[:, :, 128:].cuda(), k.cuda(), v.cuda(), lens.cuda(), 64, 1, return_lse=True)
+        assert out.shape == (2, 2, 128, D) and lse.shape == (2, 2, 128)
+        assert (out.float().cpu() - ref[:, :, 128:]).abs().max() <= tol, (dtype, D)
+
+
+def test_step_rejects_bad_shapes():
+    from kernels_b200.streaming_attention import streaming_attention_step
+
     q, k, v = (t.cuda() for t in _inputs(1, 2, 2, 256, 64, torch.float16))
     with pytest.raises(AssertionError):
         streaming_attention_step(torch.cat([q, q], dim=2), k, v, None, 64, 1)  # more queries than positions

@@ -94,12 +94,37 @@ def test_packed_against_oracle_per_sequence():
         r0 += L
 
 
-def test_packed_rejects_what_the_kernels_do_not_take():
+def test_packed_shapes_without_a_tcgen05_kernel_use_the_generic_kernels():
+    """fp32 and head dim 32: sequence by sequence through the padded operator (generic CUDA kernels), forward and
+    backward, against the oracle per sequence."""
     from kernels_b200.streaming_attention import streaming_attention_varlen
 
-    q = torch.randn(64, 2, 32, device="cuda", dtype=torch.float16)  # head_dim 32: no tcgen05 kernel
-    with pytest.raises(RuntimeError, match="unsupported"):
-        streaming_attention_varlen(q, q, q, _cu([64]), 16, 1)
+    for dtype, D, tol_o, tol_g in ((torch.float32, 64, 5e-6, 5e-5), (torch.float16, 32, 3e-3, 1e-2)):
+        H, c, back, lens = 2, 16, 2, [100, 0, 37]
+        g = torch.Generator().manual_seed(4)
+        total = sum(lens)
+        q, k, v, do = (torch.randn(total, H, D, generator=g).to(dtype) for _ in range(4))
+        qs, ks, vs = (t.cuda().requires_grad_() for t in (q, k, v))
+        out, lse = streaming_attention_varlen(qs, ks, vs, _cu(lens), c, back, return_lse=True)
+        out.backward(do.cuda())
+        assert out.shape == q.shape and lse.shape == (H, total)
+        r0 = 0
+        for L in lens:
+            if L == 0:
+                continue
+            sl = slice(r0, r0 + L)
+            qf, kf, vf = (t[sl].transpose(0, 1)[None].float().clone().requires_grad_() for t in (q, k, v))
+            ref, _, _ = SO.streaming_attention_oracle(qf, kf, vf, c, back, None)
+            ref.backward(do[sl].transpose(0, 1)[None].float())
+            assert (out[sl].detach().cpu().float().transpose(0, 1)[None] - ref.detach()).abs().max() <= tol_o
+            for gpu_grad, ref_grad in ((qs.grad, qf.grad), (ks.grad, kf.grad), (vs.grad, vf.grad)):
+                assert (gpu_grad[sl].cpu().float().transpose(0, 1)[None] - ref_grad).abs().max() <= tol_g
+            r0 += L
+
+
+def test_packed_rejects_bad_offsets():
+    from kernels_b200.streaming_attention import streaming_attention_varlen
+
     q = torch.randn(64, 2, 64, device="cuda", dtype=torch.float16)
     with pytest.raises(AssertionError):
         streaming_attention_varlen(q, q, q, _cu([60]), 16, 1)  # cu_seqlens must end at `total`
