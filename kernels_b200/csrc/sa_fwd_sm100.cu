@@ -63,7 +63,10 @@ constexpr int kThreads = (kQTiles * 4 + 2) * 32;
 constexpr int kProducerWarp = kQTiles * 4, kMmaWarp = kQTiles * 4 + 1;
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kColS = 0, kColO = 256;  // + 128 * q tile
-constexpr float kRescaleThreshold = 8.f;    // log2 units
+// Lazy rescale: the reference maximum of a row is only moved when the new maximum exceeds it by this many
+// log2 units, so P can reach 2^threshold.  16-bit P has the range for 2^8; e4m3 P (largest value 448) is formed
+// as p * 2^kFp8POffset * (v scale / largest v scale) with threshold + offset = 8, i.e. at most 256.
+constexpr float kRescaleThreshold = 8.f, kRescaleThresholdFp8 = 3.f, kFp8POffset = 5.f;
 
 struct FwdArgs {
   void* o;
@@ -349,16 +352,33 @@ sa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         KB_FACC(0);
         if (!mbar_wait(&sm.q_full, na & 1, ctx, kWaitQ)) break;
         KB_FACC(1);
-        // iteration t issues, per q tile x:  PV_x(t-1) then S_x(t)
-        for (int t = it.u_begin; ok && t <= it.u_end; ++t) {
-          const int i = t - it.u_begin;
+        // Step s issues, per q tile x:  PV_x(s - 1) then S_x(s), each q tile walking its own key tiles in order.
+        // When tile B's range starts d key tiles after tile A's (chunks shorter than the 256-row item: the two q
+        // tiles then see different windows) and the K / V rings can hold d + 1 tiles, both q tiles start at step
+        // 0 on their own first tile ("skewed": B works d key tiles ahead of A), so that every step carries both
+        // q tiles and each one's softmax overlaps the other's MMAs; otherwise B starts at step d on the tile A is
+        // on.  Either way a q tile sees its key tiles in the same order, so the results are the same bits.
+        const int n_x[kQTiles] = {it.act[0] ? it.kr[0].end - it.kr[0].begin : 0, it.act[1] ? it.kr[1].end - it.kr[1].begin : 0};
+        const int d = (it.act[0] && it.act[1]) ? it.kr[1].begin - it.kr[0].begin : 0;
+        const int first_x[kQTiles] = {0, d < kStagesK && d < kStagesV ? 0 : d};
+        const int n_steps = kb_max_i32(first_x[0] + n_x[0], first_x[1] + n_x[1]);
+        // the step at which q tile x visits key tile t (only meaningful for t inside its range)
+        auto step_of = [&](int x, int t) { return first_x[x] + t - it.kr[x].begin; };
+        // q tile x is the last of the item to use key tile t (in a matmul of the kind issued at its step)
+        auto last_user = [&](int x, int t) {
+          const int y = 1 - x;
+          if (!(it.act[y] && t >= it.kr[y].begin && t < it.kr[y].end)) return true;
+          const int sx = step_of(x, t), sy = step_of(y, t);
+          return sx > sy || (sx == sy && x > y);
+        };
+        for (int step = 0; ok && step <= n_steps; ++step) {
 #pragma unroll
           for (int x = 0; x < kQTiles; ++x) {
-            const bool pv_live = t - 1 >= it.kr[x].begin && t - 1 < it.kr[x].end;
-            const bool s_live = t >= it.kr[x].begin && t < it.kr[x].end;
+            const bool pv_live = it.act[x] && step - 1 >= first_x[x] && step - 1 < first_x[x] + n_x[x];
+            const bool s_live = it.act[x] && step >= first_x[x] && step < first_x[x] + n_x[x];
             if (pv_live) {
-              const int u = t - 1, vi = kbase + i - 1, sv = vi % kStagesV;
-              const int lx = u - it.kr[x].begin;  // index within this q tile's range
+              const int lx = step - 1 - first_x[x];  // index within this q tile's range
+              const int u = it.kr[x].begin + lx, vi = kbase + (u - it.u_begin), sv = vi % kStagesV;
               const int px = tiles_x[x] - 1;  // P block consumed now = last S block issued for x
               KB_FACC(2);
               if (!mbar_wait(&sm.p_ready[x], px & 1, ctx, kWaitPReady)) { ok = false; break; }
@@ -385,13 +405,13 @@ sa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
                 }
               }
               // V_u is free once the last q tile that uses it has consumed it
-              const bool last_user = (x == kQTiles - 1) || !(u >= it.kr[1].begin && u < it.kr[1].end);
-              if (last_user) mma_commit(&sm.v_empty[sv]);
+              if (last_user(x, u)) mma_commit(&sm.v_empty[sv]);
               if (u == it.kr[x].end - 1) mma_commit(&sm.o_done[x]);
               KB_FACC(6);
             }
             if (s_live) {
-              const int ki = kbase + i, sk = ki % kStagesK;
+              const int t = it.kr[x].begin + (step - first_x[x]);
+              const int ki = kbase + (t - it.u_begin), sk = ki % kStagesK;
               KB_FACC(2);
               if (!mbar_wait(&sm.k_full[sk], (ki / kStagesK) & 1, ctx, kWaitKFull)) { ok = false; break; }
               KB_FACC(7);
@@ -405,14 +425,13 @@ sa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
                   else mma_ss_lo(tmem + kColS + x * 128, q_lo + 2 * i, k_lo + 2 * i, idesc_qk, h > 0 || i > 0);
                 }
               }
-              const bool last_user = (x == kQTiles - 1) || !(t >= it.kr[1].begin && t < it.kr[1].end);
-              if (last_user) mma_commit(&sm.k_empty[sk]);
+              if (last_user(x, t)) mma_commit(&sm.k_empty[sk]);
               mma_commit(&sm.s_ready[x]);
               ++tiles_x[x];
               KB_FACC(8);
             }
           }
-          if (t == it.u_end - 1) mma_commit(&sm.q_empty);  // every S of this item has been issued
+          if (step == n_steps - 1) mma_commit(&sm.q_empty);  // every S of this item has been issued
         }
         kbase += it.u_end - it.u_begin;
         ++na;
@@ -463,9 +482,9 @@ sa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       }
       float m_used = -INFINITY, l = 0.f;
       // 8-bit inputs: the scores of a tile carry the scales of its q and k tiles (folded into the softmax scale);
-      // P of a tile is formed as p * 256 * (v scale of the tile) / (largest v scale of the head), which uses
-      // e4m3's range (<= 256) and lets one accumulator add tiles with different v scales: the factor enters
-      // the exponent (p_off) and is taken out of the tile's row sum again; O is divided by it at the end.
+      // P of a tile is formed as p * 2^kFp8POffset * (v scale of the tile) / (largest v scale of the head), which
+      // uses e4m3's range and lets one accumulator add tiles with different v scales: the factor enters the
+      // exponent (p_off) and is taken out of the tile's row sum again; O is divided by it at the end.
       float q_sc = 1.f, v_inv_max = 1.f, v_max = 1.f;
       const float* k_sc_row = nullptr;
       const float* v_sc_row = nullptr;
@@ -483,7 +502,7 @@ sa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         float scale = scale_base, p_off = 0.f;
         if (FP8) {
           scale = scale_base * q_sc * k_sc_row[k0 >> 7];
-          p_off = 8.f + log2f(fmaxf(v_sc_row[k0 >> 7] * v_inv_max, 9.5367431640625e-7f));  // log2(256 v / v_max)
+          p_off = kFp8POffset + log2f(fmaxf(v_sc_row[k0 >> 7] * v_inv_max, 9.5367431640625e-7f));
         }
         KB_FACC(0);
         ok = __all_sync(0xffffffffu, mbar_wait(&sm.s_ready[x], tiles & 1, ctx, kWaitSReady));
@@ -493,8 +512,8 @@ sa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         const bool warp_full = __all_sync(0xffffffffu, lo <= k0 && k0 + kBN <= hi);
         const float row_max = warp_full ? softmax_row_max<false>(t_s, k0, lo, hi) : softmax_row_max<true>(t_s, k0, lo, hi);
         const float m_new = fmaxf(m_used, row_max * scale);
-        // lazy rescale: keep the old reference maximum unless the new one is > 2^8 larger
-        const bool need = m_new > m_used + kRescaleThreshold;
+        // lazy rescale: keep the old reference maximum unless the new one is larger by more than the threshold
+        const bool need = m_new > m_used + (FP8 ? kRescaleThresholdFp8 : kRescaleThreshold);
         float alpha = 1.f;
         if (need) {
           alpha = ex2_approx(m_used - m_new);
@@ -544,7 +563,7 @@ sa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
       tc_fence_before();
       mbar_arrive(&sm.o_free[x]);
       const bool valid = qi < it.len;
-      const float inv = valid ? (FP8 ? v_max * 0.00390625f / l : 1.f / l) : 0.f;
+      const float inv = valid ? (FP8 ? v_max * exp2f(-kFp8POffset) / l : 1.f / l) : 0.f;
       // The rows leave through shared memory and a TMA store, one 64-column panel at a time (row = 128
       // bytes, 128-byte swizzle).  Plain 16-byte stores of a 256-byte row per thread touch 32 different
       // lines per instruction and held the softmax warps for several thousand clocks per item.  Rows past
