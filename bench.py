@@ -21,7 +21,7 @@ Prints ONE JSON line on rank 0:
 reference's own Triton kernel (from ``oracle/_ref``, in a child process), compiled ``flex_attention`` with
 the streaming block mask and torch SDPA with the dense mask.
 ``--workload step`` times the streaming inference step, ``--workload cfg4`` dense self-attention and softmax,
-``--workload proj`` the fused QKV + RoPE and output projections.
+``--workload proj`` the fused QKV + RoPE and output projections, ``--workload fp8`` the e4m3 forward.
 
 Multi-GPU: launched by ``torch.distributed.run`` with one rank per GPU.  The batch x heads
 slices are sharded over ranks (weak scaling for cfg3/cfg2: every rank gets a full copy of the
@@ -812,6 +812,66 @@ def run_proj(args):
     print(json.dumps(line))
 
 
+def run_fp8(args):
+    """The e4m3 forward (no counterpart in the reference's benchmarks) at the long-sequence configuration's shape: B=4
+    H=32 T=16384 D=128 context=256 back=2, lens = T; q, k, v ~ N(0, 1) quantised per tile of 128 rows.  Useful FLOPs
+    4*D*pairs; the 16-bit forward on the dequantised inputs is timed beside it.  q, k, v are 268 MB each (8-bit) plus
+    537 MB of output: more than L2, no flush."""
+    from kernels_b200 import _lib
+    from kernels_b200.sharding import useful_pairs
+    from kernels_b200.streaming_attention import (dequantize_fp8_tiles, quantize_fp8_tiles, streaming_attention,
+                                                  streaming_attention_fp8)
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    peaks = _peaks()
+    B, H, T, D, c, back = 4, 32, 16384, 128, 256, 2
+    g = torch.Generator(device=dev).manual_seed(0)
+    q8, qs = quantize_fp8_tiles(torch.randn(B, H, T, D, device=dev, generator=g))
+    k8, ks = quantize_fp8_tiles(torch.randn(B, H, T, D, device=dev, generator=g))
+    v8, vs = quantize_fp8_tiles(torch.randn(B, H, T, D, device=dev, generator=g))
+    q16, k16, v16 = (dequantize_fp8_tiles(a, b).bfloat16() for a, b in ((q8, qs), (k8, ks), (v8, vs)))
+
+    def timed(fn):
+        for _ in range(max(args.warmup, 3)):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / args.steps
+
+    launches0 = _lib.launch_count()
+    with ClockSampler(0) as clk:
+        ms8 = timed(lambda: streaming_attention_fp8(q8, k8, v8, qs, ks, vs, None, c, back))
+    launches = _lib.launch_count() - launches0
+    with torch.no_grad():
+        ms16 = timed(lambda: streaming_attention(q16, k16, v16, None, c, back))
+        o8 = streaming_attention_fp8(q8, k8, v8, qs, ks, vs, None, c, back).float()
+        o16 = streaming_attention(q16, k16, v16, None, c, back).float()
+    _lib.check_device_status()
+    rel = float((o8 - o16).norm() / o16.norm())
+    flops = 4.0 * D * B * H * useful_pairs(T, c, back)
+    line = {
+        "metric": "streaming-attn forward useful TFLOP/s, e4m3 inputs", "value": flops / ms8 / 1e9, "unit": "TFLOP/s",
+        "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms8, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "e4m3", "data": "synthetic", "impl": "kernels_b200",
+        "config": {"workload": "e4m3 q, k, v with per-128-row scales, B=4 H=32 T=16384 D=128 context=256 back=2 lens=T, forward",
+                   "name": "fp8", "l2": "inputs larger than L2 (no flush needed)"},
+        "bf16_forward_same_inputs": {"ms_per_step": ms16, "tflops": flops / ms16 / 1e9},
+        "rel_l2_vs_bf16_forward": rel,
+        "roofline": {"kernel": "sa_fwd_sm100_kernel (e4m3)", "bound": "tensor", "achieved": flops / ms8 / 1e9,
+                     "peak": 2 * peaks["tflops"], "unit": "TFLOP/s", "frac": flops / ms8 / 1e9 / (2 * peaks["tflops"]),
+                     "peak_source": peaks["source"] + " bf16 peak x 2 (8-bit instructions cover twice the reduction length)",
+                     "traffic": None, "algorithmic_flops_per_launch": flops},
+        "gpu_launches": launches, "clocks": clk.summary(),
+    }
+    print(json.dumps(line))
+
+
 def run_context(args, w):
     """Context, not an arm of the comparison: library kernels on the SAME GPU and the SAME inputs as the
     own arm (the reference's benchmark times these beside its kernel,
@@ -888,7 +948,7 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--workload", default="cfg3", choices=sorted(WORKLOADS) + ["cfg4", "step", "proj"])
+    ap.add_argument("--workload", default="cfg3", choices=sorted(WORKLOADS) + ["cfg4", "step", "proj", "fp8"])
     ap.add_argument("--impl", default="own", choices=["own", "reference", "context", "reference-triton"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
@@ -903,6 +963,8 @@ def main():
         return run_step(args)
     if args.workload == "proj":
         return run_proj(args)
+    if args.workload == "fp8":
+        return run_fp8(args)
     w = WORKLOADS[args.workload]
     if args.impl == "context":
         return run_context(args, w)
