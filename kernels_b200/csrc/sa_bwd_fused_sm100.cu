@@ -80,24 +80,6 @@ constexpr int kEpiWarp0 = 8, kProducerWarp = 12, kMmaWarp = 13, kSpillWarp = 14,
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kRelaxedNs = 0;  // poll interval of the roles off the critical chain (no gain measured from sleeping)
 constexpr uint32_t kColS = 0, kColDP = 128, kColDV = 256, kColDK = 384;
-// How the 256 compute threads announce a finished phase: every thread arrives on the barrier (0), or the
-// lanes of a warp meet and one of them arrives for all 32 (1: an eighth of the atomic updates of the barrier
-// word that the MMA thread is polling).
-#ifndef KB_WARP_ARRIVE
-#define KB_WARP_ARRIVE 0
-#endif
-constexpr uint32_t kComputeArrivals = KB_WARP_ARRIVE ? kComputeThreads / 32 : kComputeThreads;
-__device__ __forceinline__ void compute_arrive(uint64_t* bar, int lane) {
-#if KB_WARP_ARRIVE
-  __syncwarp();
-  if (lane == 0) sm100::mbar_arrive(bar);
-#else
-  (void)lane;
-  sm100::mbar_arrive(bar);
-#endif
-}
-// register budgets after the warpgroups have traded (launch budget: 128 per thread)
-constexpr int kRegsCompute = 176, kRegsEpi = 104, kRegsOther = 56;
 constexpr uint32_t kDsTileBytes = kBK * kBQ * 2;  // one dS tile: 2 panels x 128 key rows x 64 queries, 16-bit
 constexpr uint32_t kPanelBytes = 128 * 128;       // 128 rows x 128 bytes
 
@@ -281,7 +263,7 @@ sa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
       mbar_init(&sm.k_free[i], 1);
       mbar_init(&sm.q_full[i], 1);
       mbar_init(&sm.q_empty[i], 1);
-      mbar_init(&sm.ds_ready[i], kComputeArrivals);
+      mbar_init(&sm.ds_ready[i], kComputeThreads);
       mbar_init(&sm.stats_full[i], 32);
     }
     mbar_init(&sm.v_full, 1);
@@ -289,7 +271,7 @@ sa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
     mbar_init(&sm.do_full, 1);
     mbar_init(&sm.do_empty, 1);
     mbar_init(&sm.s_ready, 1);
-    mbar_init(&sm.p_ready, kComputeArrivals);
+    mbar_init(&sm.p_ready, kComputeThreads);
     mbar_init(&sm.dp_ready, 1);
     mbar_init(&sm.ds_free, 1);
     mbar_init(&sm.dv_done, 1);
@@ -619,7 +601,7 @@ sa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
       }
       tmem_wait_st();
       tc_fence_before();
-      compute_arrive(&sm.p_ready, lane);
+      mbar_arrive(&sm.p_ready);
 
       // ---- phase 2: dS = P * (dP - delta), 16-bit: over dP in TMEM (operand of dK) and into shared
       // memory (row = key, 64 queries = one 128-byte row of the thread's panel) for the scratch copy
@@ -655,7 +637,7 @@ sa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
       fence_proxy_async();  // the bulk copy reads shared memory through the async proxy
       tmem_wait_st();
       tc_fence_before();
-      compute_arrive(&sm.ds_ready[g & 1], lane);
+      mbar_arrive(&sm.ds_ready[g & 1]);
       if (threadIdx.x == 0) KB_FTR(2, g, 4);
     }
   } else {
