@@ -80,6 +80,8 @@ constexpr int kEpiWarp0 = 8, kProducerWarp = 12, kMmaWarp = 13, kSpillWarp = 14,
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kRelaxedNs = 0;  // poll interval of the roles off the critical chain (no gain measured from sleeping)
 constexpr uint32_t kColS = 0, kColDP = 128, kColDV = 256, kColDK = 384;
+// register budgets after the warpgroups have traded (launch budget: 128 per thread)
+constexpr int kRegsCompute = 176, kRegsEpi = 104, kRegsOther = 56;
 constexpr uint32_t kDsTileBytes = kBK * kBQ * 2;  // one dS tile: 2 panels x 128 key rows x 64 queries, 16-bit
 constexpr uint32_t kPanelBytes = 128 * 128;       // 128 rows x 128 bytes
 
