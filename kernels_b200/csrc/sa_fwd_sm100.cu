@@ -209,6 +209,61 @@ __device__ __forceinline__ void softmax_exp_half(uint32_t t_s, int half, float s
 
 // PACKED: one launch over a packed batch (FwdArgs::cu).  FP8: q, k, v are e4m3 with per-tile scales, both matmuls
 // run as kind::f8f6f4 (half the instructions), the output is 16-bit (BF16 selects which).
+// The same block in ONE pass for head dim 64, where the registers allow it (the epilogue holds 64 output columns,
+// not 128) and where it matters: with half the matmul work per block the softmax warps set the pace, and the
+// second walk over TMEM is time on their chain.  Loads the row's 128 scores once; returns the row maximum.
+template <bool kMasked>
+__device__ __forceinline__ float softmax_load_row_max(uint32_t t_s, uint32_t (&s)[kBN], bool (&dead)[kBN / 32], int k0, int lo, int hi) {
+#pragma unroll
+  for (int cc = 0; cc < kBN / 32; ++cc) tmem_ld32(t_s + cc * 32, reinterpret_cast<uint32_t(&)[32]>(s[cc * 32]));
+  tmem_wait_ld();
+  float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+  for (int cc = 0; cc < kBN / 32; ++cc) {
+    const int c0 = k0 + cc * 32;
+    const bool all_live = !kMasked || __all_sync(0xffffffffu, lo <= c0 && c0 + 32 <= hi);
+    dead[cc] = kMasked && __all_sync(0xffffffffu, c0 + 32 <= lo || c0 >= hi);
+    if (dead[cc]) continue;
+    if (!all_live) {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) s[cc * 32 + i] = (c0 + i >= lo && c0 + i < hi) ? s[cc * 32 + i] : 0xff800000u;  // -inf
+    }
+#pragma unroll
+    for (int i = 0; i < 32; i += 8) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+        mx[e] = fmax3(mx[e], __uint_as_float(s[cc * 32 + i + 2 * e]), __uint_as_float(s[cc * 32 + i + 2 * e + 1]));
+    }
+  }
+  return fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+}
+// ... and P = 2^(S scale - m) from the registers, 16-bit, into TMEM over S; the row sum goes into `sum`.
+template <bool BF16, bool kMasked>
+__device__ __forceinline__ void softmax_exp_held(uint32_t t_s, const uint32_t (&s)[kBN], const bool (&dead)[kBN / 32], float scale,
+                                                 float m_used, float (&sum)[4]) {
+  const float m_safe = (m_used == -INFINITY) ? 0.f : m_used;
+#pragma unroll
+  for (int cc = 0; cc < kBN / 32; ++cc) {
+    uint32_t pk[16];
+    if (kMasked && dead[cc]) {
+#pragma unroll
+      for (int i = 0; i < 16; ++i) pk[i] = 0u;
+      tmem_st16(t_s + cc * 16, pk);
+      continue;
+    }
+    // scalar arithmetic here: with 128 scores held, the register pairs of the packed form do not fit
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const float p0 = ex2_approx(fmaf(__uint_as_float(s[cc * 32 + 2 * i]), scale, -m_safe));
+      const float p1 = ex2_approx(fmaf(__uint_as_float(s[cc * 32 + 2 * i + 1]), scale, -m_safe));
+      sum[(2 * i) & 3] += p0;
+      sum[(2 * i + 1) & 3] += p1;
+      pk[i] = pack16x2<BF16>(p0, p1);
+    }
+    tmem_st16(t_s + cc * 16, pk);
+  }
+}
+
 template <int D, bool BF16, bool PACKED, bool FP8>
 __global__ void __launch_bounds__(kThreads, 1)
 sa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
@@ -510,7 +565,16 @@ sa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         tc_fence_after();
         KB_FACC(1);
         const bool warp_full = __all_sync(0xffffffffu, lo <= k0 && k0 + kBN <= hi);
-        const float row_max = warp_full ? softmax_row_max<false>(t_s, k0, lo, hi) : softmax_row_max<true>(t_s, k0, lo, hi);
+        constexpr bool kHold = (D == 64) && !FP8;  // one pass with the row's scores held in registers
+        uint32_t s_held[kHold ? kBN : 1];
+        bool dead_held[kBN / 32];
+        float row_max;
+        if (kHold) {
+          row_max = warp_full ? softmax_load_row_max<false>(t_s, reinterpret_cast<uint32_t(&)[kBN]>(s_held), dead_held, k0, lo, hi)
+                              : softmax_load_row_max<true>(t_s, reinterpret_cast<uint32_t(&)[kBN]>(s_held), dead_held, k0, lo, hi);
+        } else {
+          row_max = warp_full ? softmax_row_max<false>(t_s, k0, lo, hi) : softmax_row_max<true>(t_s, k0, lo, hi);
+        }
         const float m_new = fmaxf(m_used, row_max * scale);
         // lazy rescale: keep the old reference maximum unless the new one is larger by more than the threshold
         const bool need = m_new > m_used + (FP8 ? kRescaleThresholdFp8 : kRescaleThreshold);
@@ -521,6 +585,20 @@ sa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
           l *= alpha;
         }
         KB_FACC(2);
+        KB_FACC(3);
+        float sum[4] = {0.f, 0.f, 0.f, 0.f};
+        const float m_exp = m_used - p_off;  // 2^(s scale - m_exp) = p * 2^p_off
+        if (kHold) {
+          if (warp_full) softmax_exp_held<BF16, false>(t_s, reinterpret_cast<const uint32_t(&)[kBN]>(s_held), dead_held, scale, m_exp, sum);
+          else softmax_exp_held<BF16, true>(t_s, reinterpret_cast<const uint32_t(&)[kBN]>(s_held), dead_held, scale, m_exp, sum);
+        } else {
+          if (warp_full) softmax_exp_half<BF16, false, FP8>(t_s, 0, scale, m_exp, k0, lo, hi, sum);
+          else softmax_exp_half<BF16, true, FP8>(t_s, 0, scale, m_exp, k0, lo, hi, sum);
+          if (warp_full) softmax_exp_half<BF16, false, FP8>(t_s, 1, scale, m_exp, k0, lo, hi, sum);
+          else softmax_exp_half<BF16, true, FP8>(t_s, 1, scale, m_exp, k0, lo, hi, sum);
+        }
+        // the rescale of O comes after the exponentials: the row's scores are dead by now, which keeps the
+        // registers of the two from being live together
         if (lx > 0 && __any_sync(0xffffffffu, need)) {
           // S(lx) is complete, so the P V of the previous tile (issued before it) is too: O is idle
 #pragma unroll
@@ -533,13 +611,6 @@ sa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
             tmem_st32(t_o + cc * 32, r);
           }
         }
-        KB_FACC(3);
-        float sum[4] = {0.f, 0.f, 0.f, 0.f};
-        const float m_exp = m_used - p_off;  // 2^(s scale - m_exp) = p * 2^p_off
-        if (warp_full) softmax_exp_half<BF16, false, FP8>(t_s, 0, scale, m_exp, k0, lo, hi, sum);
-        else softmax_exp_half<BF16, true, FP8>(t_s, 0, scale, m_exp, k0, lo, hi, sum);
-        if (warp_full) softmax_exp_half<BF16, false, FP8>(t_s, 1, scale, m_exp, k0, lo, hi, sum);
-        else softmax_exp_half<BF16, true, FP8>(t_s, 1, scale, m_exp, k0, lo, hi, sum);
         tmem_wait_st();
         tc_fence_before();
         mbar_arrive(&sm.p_ready[x]);
