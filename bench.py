@@ -206,16 +206,29 @@ def _cpu_baseline(w, steps, warmup, budget_s=25.0):
                        f"{statistics.mean(times) * 1e3:.0f} ms per slice"), statistics.mean(times) * 1e3
 
 
+def _config_block(w, name, world):
+    """The ``config`` of a bench line: the same for the own arm and the reference arm of one launch."""
+    B, lens = _global_problem(w, world)
+    H, T, D = w["H"], w["T"], w["D"]
+    pairs_total, _ = _useful_pairs_total(w, B, lens, H)
+    tensor_bytes = B * (H // world) * T * D * torch.empty(0, dtype=TORCH_DTYPES[w["dtype"]]).element_size()
+    return {"workload": w["desc"], "name": name, "global_batch": B, "heads_per_gpu": H // world,
+            "sharding": f"batch x heads, heads round-robin over {world} GPU(s), no collective",
+            "l2": "inputs larger than L2 (no flush needed)" if 4 * tensor_bytes > 4 * 126e6 else "L2 not flushed",
+            "useful_flops_per_step": 14.0 * D * pairs_total}
+
+
 def run_reference(args, w):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     base, ms = _cpu_baseline(w, args.steps, args.warmup, budget_s=None)
+    base["sample"] += "; one (batch, head) slice per step on the host cores"
     line = {
         "impl": "reference", "metric": "streaming-attn fwd+bwd useful TFLOP/s", "value": base["value"],
         "unit": "TFLOP/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
         "higher_is_better": True, "scaling": w["scaling"], "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": w["desc"], "step": "one (batch, head) slice per step on the host cores"},
+        "config": _config_block(w, args.workload, args.gpus),
         "cpu_baseline": base,
         "e2e": {"value": base["value"], "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -464,10 +477,7 @@ def run_own(args, w):
             "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step,
             "higher_is_better": True, "scaling": w["scaling"], "vs_baseline": None, "dtype": w["dtype"],
             "data": "synthetic", "impl": "kernels_b200",
-            "config": {"workload": w["desc"], "name": args.workload, "global_batch": B, "heads_per_gpu": len(heads),
-                       "sharding": f"batch x heads, heads round-robin over {world} GPU(s), no collective",
-                       "l2": "inputs larger than L2 (no flush needed)" if 4 * tensor_bytes > 4 * 126e6 else "L2 not flushed",
-                       "useful_flops_per_step": flops_total},
+            "config": _config_block(w, args.workload, world),
             "per_gpu_tflops": value / world,
             "frac_of_bf16_peak": {"measured_burst": value / world / peaks["tflops"],
                                   "measured_sustained": value / world / peaks["tflops_sustained"],
