@@ -65,9 +65,11 @@ struct WaitCtx {
   int32_t* status;           // global / pinned host, may be null
 };
 
+// The first wait of a CTA to give up is the one that reports: the others run out soon after it only because
+// it stopped, and their sites would say nothing about the cause.
 static __device__ __noinline__ bool mbar_give_up(volatile int* abort_flag, int32_t* status, int where) {
-  *abort_flag = 1;
-  if (status) {
+  const bool first = atomicExch(const_cast<int*>(abort_flag), 1) == 0;
+  if (status && first) {
     atomicExch(status, KB_ERR_DEVICE_TIMEOUT);
     atomicExch(status + 1, where);
     atomicExch(status + 2, (int)blockIdx.x);
