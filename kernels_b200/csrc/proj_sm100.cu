@@ -9,15 +9,20 @@
 // The reference project has neither (its callers run torch.nn.Linear around the operator); the seam is its
 // public call, src/streaming_attention/kernel.py:1599-1652 (inputs q, k, v [B, H, T, D], output O).
 //
-// One kernel template.  A tile is 128 tokens x 256 output features: the M128 N256 K16 tcgen05.mma takes 128
-// clocks, so one issuing thread keeps the tensor pipe fed with room to spare.  The reduction runs in
-// steps of 64 elements (one 128-byte swizzled panel per row): per step the producer brings a 16 KB tile of the
-// activation and a 32 KB tile of the weight into a four-stage ring with TMA, the MMA thread issues four
-// instructions.  The fp32 accumulator (256 TMEM columns) is double buffered, so the four epilogue warps
-// (thread = token row = TMEM lane) convert, rotate, stage and TMA-store a finished tile while the next one
-// is being accumulated.  Persistent: one CTA per SM walks the tiles, feature tiles fastest, so CTAs running
-// at the same time share activation tiles in L2 (the weight is read once per wave and stays in L2).
-// Bound: tensor pipe, then L2 -> SM bandwidth (48 KB per 512 clocks per SM).
+// One kernel template, run by CTA pairs (clusters of 2, `tcgen05.mma.cta_group::2`).  A pair's tile is 256 tokens x
+// 256 output features: CTA r of the pair owns tokens [128 r, 128 r + 128) of it (its A rows, its accumulator rows,
+// its epilogue) and brings in half of the weight tile (feature rows [128 r, 128 r + 128)); the M256 N256 K16
+// instruction, issued by one thread of the pair's leader, takes 128 clocks on each SM, so that thread keeps both
+// tensor pipes fed with room to spare, and each SM fetches 8 KB of operands per instruction from its shared memory
+// instead of the 12 KB a single-CTA M128 N256 instruction needs.  The reduction runs in steps of 64 elements (one
+// 128-byte swizzled panel per row): per step each CTA's producer brings its 16 KB activation tile and its 16 KB half of
+// the weight tile into a six-stage ring with TMA, the peer's MMA warp forwards "my tiles of this stage have
+// landed" to the leader's barrier, and the leader's MMA thread issues four instructions; its commits arrive on
+// the barriers of both CTAs.  The fp32 accumulator (256 TMEM columns in each CTA) is double buffered, so the four
+// epilogue warps of each CTA (thread = token row = TMEM lane) convert, rotate, stage and TMA-store a finished
+// tile while the next one is being accumulated.  Persistent: one pair per two SMs walks the tiles, feature tiles
+// fastest, so pairs running at the same time share activation tiles in L2 (the weight is read once per wave and
+// stays in L2).  Bound: tensor pipe.
 //
 // Rotary embedding, "rotate half" convention: for a head's element pair (d, d + D/2) at position t
 //   out[d] = a[d] cos(t, d) - a[d + D/2] sin(t, d),   out[d + D/2] = a[d + D/2] cos(t, d) + a[d] sin(t, d),
@@ -37,16 +42,16 @@ using namespace sm100;
 constexpr int kPM = 128;  // tokens per tile
 constexpr int kPN = 256;  // output features per tile
 constexpr int kPK = 64;   // reduction elements per stage
-constexpr int kPStages = 4;
+constexpr int kPStages = 6;
 constexpr int kPThreads = 192;
 constexpr int kPProducerWarp = 4, kPMmaWarp = 5;
 constexpr uint32_t kPTmemCols = 512;  // two accumulators of 256 columns
-constexpr uint32_t kPATileBytes = kPM * kPK * 2, kPBTileBytes = kPN * kPK * 2;
+constexpr uint32_t kPATileBytes = kPM * kPK * 2, kPBTileBytes = (kPN / 2) * kPK * 2;  // per CTA: its tokens, its half of the features
 constexpr uint32_t kPPanelBytes = 128 * 128;  // 128 rows x 128 bytes
 
 struct ProjArgs {
   int32_t B, T;             // batch entries, tokens per entry
-  int32_t n_mt, n_nt;       // token tiles per batch entry, feature tiles
+  int32_t n_mt, n_nt;       // token tiles OF A PAIR (256 tokens) per batch entry, feature tiles
   int32_t k_steps;          // reduction steps of 64 elements
   int32_t a_inner_steps;    // steps per A "head": E / 64 for x, D / 64 for o (the A map's third coordinate counts heads)
   // output: feature tile nt covers features [256 nt, 256 nt + 256) = 256 / D heads of the stacked q | k | v
@@ -67,11 +72,11 @@ struct alignas(1024) ProjSmem {
   int abort_flag;
 };
 
-enum WaitSite { kWPEmpty = 101, kWPFull, kWPAccFree, kWPAccDone };
+enum WaitSite { kWPEmpty = 101, kWPFull, kWPAccFree, kWPAccDone, kWPForward };
 constexpr int kErrSmemAlign = 111;
 
 template <bool BF16>
-__global__ void __launch_bounds__(kPThreads, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPThreads, 1)
 proj_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                   const __grid_constant__ CUtensorMap tm_o0, const __grid_constant__ CUtensorMap tm_o1,
                   const __grid_constant__ CUtensorMap tm_o2, const ProjArgs a) {
@@ -79,8 +84,10 @@ proj_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
   ProjSmem& sm = *reinterpret_cast<ProjSmem*>(smem_raw);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_items = a.B * a.n_mt * a.n_nt;
+  const uint32_t rank = cluster_ctarank();              // 0: the pair's leader
+  const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
 
-  if (smem_u32(smem_raw) & 1023u) {
+  if (smem_u32(smem_raw) & 1023u) {  // (the same in both CTAs of a pair)
     if (threadIdx.x == 0 && a.status) {
       atomicExch(a.status, KB_ERR_DEVICE_TIMEOUT);
       atomicExch(a.status + 1, kErrSmemAlign);
@@ -89,29 +96,32 @@ proj_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
   }
   if (threadIdx.x == 0) {
     for (int s = 0; s < kPStages; ++s) {
-      mbar_init(&sm.full[s], 1);
+      // the leader's: its own producer (with the bytes of its two tiles) and the peer's forwarded arrival
+      mbar_init(&sm.full[s], rank == 0 ? 2 : 1);
       mbar_init(&sm.empty[s], 1);
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&sm.acc_done[i], 1);
-      mbar_init(&sm.acc_free[i], 128);
+      mbar_init(&sm.acc_free[i], 256);  // the leader's is the one used: the epilogue threads of both CTAs arrive on it
     }
     sm.abort_flag = 0;
     fence_mbar_init();
   }
-  if (warp == kPMmaWarp) tmem_alloc(&sm.tmem_base, kPTmemCols);
+  __syncthreads();
+  if (warp == kPMmaWarp) tmem_alloc_pair(&sm.tmem_base, kPTmemCols);
   tc_fence_before();
   __syncthreads();
+  cluster_sync_all();  // both CTAs' barriers are initialised before either arrives on the other's
   tc_fence_after();
   const uint32_t tmem = sm.tmem_base;
   const WaitCtx ctx{&sm.abort_flag, a.status};
 
-  // item -> (batch entry, token tile, feature tile), feature tile fastest
+  // item -> (batch entry, token tile of the pair, feature tile), feature tile fastest
   auto decode = [&](int item, int& b, int& mt, int& nt) {
     const int bm = kb_fastdiv(item, a.fd_nt);
     nt = item - bm * a.n_nt;
     b = kb_fastdiv(bm, a.fd_mt);
-    mt = bm - b * a.n_mt;
+    mt = 2 * (bm - b * a.n_mt) + (int)rank;  // this CTA's tile of 128 tokens
   };
 
   if (warp == kPProducerWarp) {
@@ -120,7 +130,7 @@ proj_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       prefetch_tensormap(&tm_b);
       int u = 0;  // stages filled so far
       bool ok = true;
-      for (int item = blockIdx.x; ok && item < n_items; item += gridDim.x) {
+      for (int item = pair; ok && item < n_items; item += n_pairs) {
         int b, mt, nt;
         decode(item, b, mt, nt);
         int inner = 0, head = 0;  // position of the step inside A: element 64 * inner of "head" `head`
@@ -129,7 +139,7 @@ proj_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
           if (u >= kPStages && !mbar_wait(&sm.empty[s], ((u / kPStages) - 1) & 1, ctx, kWPEmpty)) { ok = false; break; }
           mbar_expect_tx(&sm.full[s], kPATileBytes + kPBTileBytes);
           tma_load_4d(sm.a[s], &tm_a, &sm.full[s], inner * kPK, mt * kPM, head, b);
-          tma_load_4d(sm.b[s], &tm_b, &sm.full[s], kk * kPK, nt * kPN, 0, 0);
+          tma_load_4d(sm.b[s], &tm_b, &sm.full[s], kk * kPK, nt * kPN + (int)rank * (kPN / 2), 0, 0);
           if (++inner == a.a_inner_steps) {
             inner = 0;
             ++head;
@@ -138,11 +148,12 @@ proj_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
       }
     }
   } else if (warp == kPMmaWarp) {
-    if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc(BF16, kPM, kPN, false, false);
+    if (lane == 0 && rank == 0) {
+      // ------------------------------ MMA issuer (leader) ------------------------------
+      constexpr uint32_t idesc = make_idesc(BF16, 2 * kPM, kPN, false, false);
       int u = 0, m = 0;  // stages consumed, tiles so far
       bool ok = true;
-      for (int item = blockIdx.x; ok && item < n_items; item += gridDim.x, ++m) {
+      for (int item = pair; ok && item < n_items; item += n_pairs, ++m) {
         const uint32_t acc = tmem + (uint32_t)(m & 1) * kPN;
         if (m >= 2 && !mbar_wait(&sm.acc_free[m & 1], ((m >> 1) - 1) & 1, ctx, kWPAccFree)) break;
         tc_fence_after();
@@ -152,10 +163,21 @@ proj_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
           tc_fence_after();
           const uint32_t a_lo = desc_lo_kmajor(smem_u32(sm.a[s])), b_lo = desc_lo_kmajor(smem_u32(sm.b[s]));
 #pragma unroll
-          for (int i = 0; i < kPK / 16; ++i) mma_ss_lo(acc, a_lo + 2 * i, b_lo + 2 * i, idesc, kk > 0 || i > 0);
-          mma_commit(&sm.empty[s]);
+          for (int i = 0; i < kPK / 16; ++i) mma_ss_lo_pair(acc, a_lo + 2 * i, b_lo + 2 * i, idesc, kk > 0 || i > 0);
+          mma_commit_pair(&sm.empty[s]);
         }
-        if (ok) mma_commit(&sm.acc_done[m & 1]);
+        if (ok) mma_commit_pair(&sm.acc_done[m & 1]);
+      }
+    } else if (lane == 0) {
+      // ------------------------------ peer: tiles landed -> the leader's barrier ------------------------------
+      int u = 0;
+      bool ok = true;
+      for (int item = pair; ok && item < n_items; item += n_pairs) {
+        for (int kk = 0; kk < a.k_steps; ++kk, ++u) {
+          const int s = u % kPStages;
+          if (!mbar_wait(&sm.full[s], (u / kPStages) & 1, ctx, kWPForward)) { ok = false; break; }
+          mbar_arrive_cluster(&sm.full[s], 0);
+        }
       }
     }
   } else {
@@ -165,7 +187,7 @@ proj_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     const int D = a.D;
     int m = 0;
     bool ok = true;
-    for (int item = blockIdx.x; ok && item < n_items; item += gridDim.x, ++m) {
+    for (int item = pair; ok && item < n_items; item += n_pairs, ++m) {
       int b, mt, nt;
       decode(item, b, mt, nt);
       const int t = mt * kPM + row;  // this thread's token
@@ -204,7 +226,7 @@ proj_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
           tmem_wait_ld();
           if (g == kPN / 128 - 1 && j == 1) {
             tc_fence_before();
-            mbar_arrive(&sm.acc_free[m & 1]);  // the accumulator may be overwritten by the tile after next
+            mbar_arrive_cluster(&sm.acc_free[m & 1], 0);  // (the leader's barrier) the accumulator may be overwritten by the tile after next
           }
           if (rope && t < a.T) {
             const float* cs = a.rope_cos + (int64_t)i0 * a.T + t;
@@ -237,7 +259,7 @@ proj_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         }
         fence_proxy_async();
         named_barrier_sync(2, 128);
-        if (threadIdx.x == 0) {
+        if (threadIdx.x == 0 && mt * kPM < a.T) {  // (the second tile of a pair may lie wholly past the last token)
           const CUtensorMap* tm = which == 0 ? &tm_o0 : (which == 1 ? &tm_o1 : &tm_o2);
           if (D == 0) {
             // plain output [B, T, E_out]: the group's 128 columns are two 64-column boxes
@@ -257,11 +279,14 @@ proj_sm100_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     if (threadIdx.x == 0) tma_store_wait_all();
   }
 
+  // neither CTA leaves, nor gives its TMEM back, while the other may still read its shared memory or arrive on
+  // its barriers
   tc_fence_before();
   __syncthreads();
+  cluster_sync_all();
   if (warp == kPMmaWarp) {
     if (sm.abort_flag) __nanosleep(1000000);  // let copies still in flight land before the CTA goes away
-    tmem_dealloc(tmem, kPTmemCols);
+    tmem_dealloc_pair(tmem, kPTmemCols);
   }
 }
 
@@ -284,7 +309,29 @@ int launch_proj(const CUtensorMap& tm_a, const CUtensorMap& tm_b, const CUtensor
   KB_CUDA_TRY(opt_in_smem_once(kern, sizeof(ProjSmem), dev, smem_opted_in));
   const int64_t n_items = (int64_t)a.B * a.n_mt * a.n_nt;
   if (n_items > (int64_t)1 << 30) return KB_ERR_TOO_LARGE;
-  const unsigned grid = (unsigned)(n_items < n_sm ? n_items : n_sm);
+  // Persistent: as many pairs as the device can hold at once (not every SM of a die can be paired up, so this
+  // may be fewer than half the SM count; a grid larger than that would run its last pairs as a second wave).
+  static std::atomic<int> pairs_cached[kMaxDevices];
+  int max_pairs = pairs_cached[dev].load(std::memory_order_relaxed);
+  if (max_pairs == 0) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(n_sm & ~1), 1, 1);
+    cfg.blockDim = dim3(kPThreads, 1, 1);
+    cfg.dynamicSmemBytes = sizeof(ProjSmem);
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2, attr.val.clusterDim.y = 1, attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n < 1) {
+      (void)cudaGetLastError();
+      n = n_sm / 2;
+    }
+    max_pairs = n < n_sm / 2 ? n : n_sm / 2;
+    pairs_cached[dev].store(max_pairs, std::memory_order_relaxed);
+  }
+  const unsigned grid = 2u * (unsigned)(n_items < max_pairs ? n_items : max_pairs);
   kern<<<grid, kPThreads, sizeof(ProjSmem), s>>>(tm_a, tm_b, o0, o1, o2, a);
   KB_LAUNCH_CHECK("proj_sm100_kernel");
   return KB_OK;
@@ -317,14 +364,14 @@ extern "C" int kb_qkv_rope_proj(const kb_qkv_proj_params* p, void* stream) {
   xv.stride[0] = (int64_t)p->T * p->E, xv.stride[1] = 0, xv.stride[2] = p->E, xv.stride[3] = 1;
   const int64_t none[3] = {0, 0, 0};
   if (!make_tile_map_4d(&tm_a, xv, p->B, 1, p->T, p->E, kPM) ||
-      !make_tile_map_4d(&tm_b, matrix_view(p->w, p->E), 1, 1, (int)n_feat, p->E, kPN) ||
+      !make_tile_map_4d(&tm_b, matrix_view(p->w, p->E), 1, 1, (int)n_feat, p->E, kPN / 2) ||
       !make_tile_map_4d(&tm_q, out_view(p->q, none, p->H, p->T, p->D), p->B, p->H, p->T, p->D, kPM) ||
       !make_tile_map_4d(&tm_k, out_view(p->k, none, p->H_kv, p->T, p->D), p->B, p->H_kv, p->T, p->D, kPM) ||
       !make_tile_map_4d(&tm_v, out_view(p->v, none, p->H_kv, p->T, p->D), p->B, p->H_kv, p->T, p->D, kPM))
     return KB_ERR_UNSUPPORTED;
   ProjArgs a;
   a.B = p->B, a.T = p->T;
-  a.n_mt = kb_cdiv_i32(p->T, kPM);
+  a.n_mt = kb_cdiv_i32(p->T, 2 * kPM);
   a.n_nt = (int32_t)(n_feat / kPN);
   a.k_steps = p->E / kPK;
   a.a_inner_steps = a.k_steps;
@@ -353,12 +400,12 @@ extern "C" int kb_out_proj(const kb_out_proj_params* p, void* stream) {
   yv.data = p->y;
   yv.stride[0] = (int64_t)p->T * p->E_out, yv.stride[1] = 0, yv.stride[2] = p->E_out, yv.stride[3] = 1;
   if (!make_tile_map_4d(&tm_a, p->o, p->B, p->H, p->T, p->D, kPM) ||
-      !make_tile_map_4d(&tm_b, matrix_view(p->w, (int64_t)p->H * p->D), 1, 1, p->E_out, p->H * p->D, kPN) ||
+      !make_tile_map_4d(&tm_b, matrix_view(p->w, (int64_t)p->H * p->D), 1, 1, p->E_out, p->H * p->D, kPN / 2) ||
       !make_tile_map_4d(&tm_y, yv, p->B, 1, p->T, p->E_out, kPM))
     return KB_ERR_UNSUPPORTED;
   ProjArgs a;
   a.B = p->B, a.T = p->T;
-  a.n_mt = kb_cdiv_i32(p->T, kPM);
+  a.n_mt = kb_cdiv_i32(p->T, 2 * kPM);
   a.n_nt = p->E_out / kPN;
   a.k_steps = p->H * p->D / kPK;
   a.a_inner_steps = p->D / kPK;

@@ -320,6 +320,52 @@ __device__ __forceinline__ void mma_commit(uint64_t* bar) {
                : "memory");
 }
 
+// ---- CTA pairs (cta_group::2) -----------------------------------------------------------------
+// Two CTAs of a cluster of 2 share one MMA: the instruction, issued by ONE thread of the pair's leader (cluster
+// rank 0), multiplies M = 256 rows, 128 from each CTA's shared memory at the same offset, by a B operand of which
+// each CTA holds half of the N rows, and leaves each CTA's 128 accumulator rows in its own TMEM at the same
+// address.  TMEM is allocated by one warp of EACH CTA executing the same alloc (both get the same address).
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// every thread of both CTAs
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_result, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_result)), "r"(ncols)
+               : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void mma_ss_lo_pair(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc, bool accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "mov.b64 da, {%1, %5};\n\tmov.b64 db, {%2, %5};\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(idesc), "r"((uint32_t)accumulate), "r"(kDescHiSw128)
+      : "memory");
+}
+// Arrive on the barrier at `bar`'s offset in BOTH CTAs once every MMA issued so far by this thread has completed.
+__device__ __forceinline__ void mma_commit_pair(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
+                   smem_u32(bar)),
+               "h"((uint16_t)3)
+               : "memory");
+}
+// Arrive on the barrier at `bar`'s offset in CTA `rank` of the cluster.  What these arrivals order are tile copies
+// and TMEM accesses (async proxy, tcgen05 fences), not generic-proxy data, so the waiter uses the ordinary wait:
+// a wait with `.acquire.cluster` on every reduction step measured TWICE the run time of the whole GEMM.
+__device__ __forceinline__ void mbar_arrive_cluster(uint64_t* bar, uint32_t rank) {
+  asm volatile(
+      "{\n\t.reg .b32 ra;\n\tmapa.shared::cluster.u32 ra, %0, %1;\n\t"
+      "mbarrier.arrive.shared::cluster.b64 _, [ra];\n\t}" ::"r"(smem_u32(bar)), "r"(rank)
+      : "memory");
+}
 // ---- register budget of a warpgroup ------------------------------------------------------
 // A kernel whose warpgroups have very different register needs starts every thread with the
 // launch-bound budget and lets each warpgroup trade: all four warps of the warpgroup execute

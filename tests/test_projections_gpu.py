@@ -33,6 +33,7 @@ def _close(name, got, ref):
     (2, 200, 192, 8, 4, 64, torch.bfloat16, True),      # four heads per feature tile
     (1, 513, 320, 4, 4, 64, torch.float16, False),      # no rotation
     (3, 1, 128, 2, 2, 128, torch.bfloat16, True),       # one token
+    (2, 2048, 512, 8, 4, 128, torch.bfloat16, True),    # more tiles than CTA pairs, more reduction steps than ring stages
 ])
 def test_qkv_rope_projection_matches_oracle(B, T, E, H, Hk, D, dtype, rope):
     from kernels_b200.streaming_attention import qkv_rope_projection, rope_tables
@@ -55,6 +56,7 @@ def test_qkv_rope_projection_matches_oracle(B, T, E, H, Hk, D, dtype, rope):
     (2, 300, 4, 128, 512, torch.bfloat16, False),
     (1, 129, 6, 64, 256, torch.float16, False),
     (2, 256, 2, 128, 256, torch.bfloat16, True),   # o as a [B, T, H, D] buffer viewed as [B, H, T, D]
+    (3, 1500, 8, 128, 1024, torch.bfloat16, False),  # more tiles than CTA pairs, a last pair with one tile
 ])
 def test_output_projection_matches_oracle(B, T, H, D, E_out, dtype, strided):
     from kernels_b200.streaming_attention import output_projection
