@@ -426,67 +426,137 @@ sa_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
           const int sx = step_of(x, t), sy = step_of(y, t);
           return sx > sy || (sx == sy && x > y);
         };
-        for (int step = 0; ok && step <= n_steps; ++step) {
+        // O_x (+)= P_x V of the q tile's lx-th key tile, V being ring tile vi (counted over the CTA's life)
+        auto issue_pv = [&](int x, int lx, int vi, bool release_v, bool last_tile) -> bool {
+          const int sv = vi % kStagesV;
+          const int px = tiles_x[x] - 1;  // P block consumed now = last S block issued for x
+          KB_FACC(2);
+          if (!mbar_wait(&sm.p_ready[x], px & 1, ctx, kWaitPReady)) return false;
+          KB_FACC(3 + x);
+          if (!mbar_wait(&sm.v_full[sv], (vi / kStagesV) & 1, ctx, kWaitVFull)) return false;
+          KB_FACC(5);
+          // the first P V of an item overwrites O: the softmax warps must have read the old one
+          if (lx == 0 && items_x[x] > 0 && !mbar_wait(&sm.o_free[x], (items_x[x] - 1) & 1, ctx, kWaitOFree)) return false;
+          tc_fence_after();
+          // short issue loops (four instructions per trip, descriptor low words stepped by adds): the
+          // scalar work between two MMAs is what the tensor pipe waits for
+          uint32_t p_col = tmem + kColS + x * 128, v_lo = desc_lo_mnmajor(smem_u32(sm.v[sv]), kPanelBytes);
+          if (FP8) {
+            // 128 keys = four instructions of 32 keys: 8 packed columns of P, 32 rows (4096 bytes) of V each
 #pragma unroll
-          for (int x = 0; x < kQTiles; ++x) {
-            const bool pv_live = it.act[x] && step - 1 >= first_x[x] && step - 1 < first_x[x] + n_x[x];
-            const bool s_live = it.act[x] && step >= first_x[x] && step < first_x[x] + n_x[x];
-            if (pv_live) {
-              const int lx = step - 1 - first_x[x];  // index within this q tile's range
-              const int u = it.kr[x].begin + lx, vi = kbase + (u - it.u_begin), sv = vi % kStagesV;
-              const int px = tiles_x[x] - 1;  // P block consumed now = last S block issued for x
-              KB_FACC(2);
-              if (!mbar_wait(&sm.p_ready[x], px & 1, ctx, kWaitPReady)) { ok = false; break; }
-              KB_FACC(3 + x);
-              if (!mbar_wait(&sm.v_full[sv], (vi / kStagesV) & 1, ctx, kWaitVFull)) { ok = false; break; }
-              KB_FACC(5);
-              // the first P V of an item overwrites O: the softmax warps must have read the old one
-              if (lx == 0 && items_x[x] > 0 && !mbar_wait(&sm.o_free[x], (items_x[x] - 1) & 1, ctx, kWaitOFree)) { ok = false; break; }
-              tc_fence_after();
-              // short issue loops (four instructions per trip, descriptor low words stepped by adds): the
-              // scalar work between two MMAs is what the tensor pipe waits for
-              uint32_t p_col = tmem + kColS + x * 128, v_lo = desc_lo_mnmajor(smem_u32(sm.v[sv]), kPanelBytes);
-              if (FP8) {
-                // 128 keys = four instructions of 32 keys: 8 packed columns of P, 32 rows (4096 bytes) of V each
-#pragma unroll
-                for (int i = 0; i < 4; ++i)
-                  mma_ts_lo_f8(tmem + kColO + x * 128, p_col + 8 * i, v_lo + i * (4096 >> 4), idesc_pv, lx > 0 || i > 0);
-              } else {
+            for (int i = 0; i < 4; ++i)
+              mma_ts_lo_f8(tmem + kColO + x * 128, p_col + 8 * i, v_lo + i * (4096 >> 4), idesc_pv, lx > 0 || i > 0);
+          } else {
 #pragma unroll 1
-                for (int h = 0; h < kBN / 64; ++h, p_col += 32, v_lo += 4 * (2048 >> 4)) {
+            for (int h = 0; h < kBN / 64; ++h, p_col += 32, v_lo += 4 * (2048 >> 4)) {
 #pragma unroll
-                  for (int i = 0; i < 4; ++i)
-                    mma_ts_lo(tmem + kColO + x * 128, p_col + 8 * i, v_lo + i * (2048 >> 4), idesc_pv, lx > 0 || h > 0 || i > 0);
-                }
-              }
-              // V_u is free once the last q tile that uses it has consumed it
-              if (last_user(x, u)) mma_commit(&sm.v_empty[sv]);
-              if (u == it.kr[x].end - 1) mma_commit(&sm.o_done[x]);
-              KB_FACC(6);
-            }
-            if (s_live) {
-              const int t = it.kr[x].begin + (step - first_x[x]);
-              const int ki = kbase + (t - it.u_begin), sk = ki % kStagesK;
-              KB_FACC(2);
-              if (!mbar_wait(&sm.k_full[sk], (ki / kStagesK) & 1, ctx, kWaitKFull)) { ok = false; break; }
-              KB_FACC(7);
-              tc_fence_after();
-              uint32_t q_lo = desc_lo_kmajor(smem_u32(sm.q[x])), k_lo = desc_lo_kmajor(smem_u32(sm.k[sk]));
-#pragma unroll 1
-              for (int h = 0; h < kPanels; ++h, q_lo += kPanelBytes >> 4, k_lo += kPanelBytes >> 4) {
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {  // 32 bytes of every row per instruction: 16 16-bit or 32 8-bit elements
-                  if (FP8) mma_ss_lo_f8(tmem + kColS + x * 128, q_lo + 2 * i, k_lo + 2 * i, idesc_qk, h > 0 || i > 0);
-                  else mma_ss_lo(tmem + kColS + x * 128, q_lo + 2 * i, k_lo + 2 * i, idesc_qk, h > 0 || i > 0);
-                }
-              }
-              if (last_user(x, t)) mma_commit(&sm.k_empty[sk]);
-              mma_commit(&sm.s_ready[x]);
-              ++tiles_x[x];
-              KB_FACC(8);
+              for (int i = 0; i < 4; ++i)
+                mma_ts_lo(tmem + kColO + x * 128, p_col + 8 * i, v_lo + i * (2048 >> 4), idesc_pv, lx > 0 || h > 0 || i > 0);
             }
           }
-          if (step == n_steps - 1) mma_commit(&sm.q_empty);  // every S of this item has been issued
+          if (release_v) mma_commit(&sm.v_empty[sv]);  // V is free once the last q tile that uses it has consumed it
+          if (last_tile) mma_commit(&sm.o_done[x]);
+          KB_FACC(6);
+          return true;
+        };
+        // S_x = Q_x K^T, K being ring tile ki
+        auto issue_s = [&](int x, int ki, bool release_k) -> bool {
+          const int sk = ki % kStagesK;
+          KB_FACC(2);
+          if (!mbar_wait(&sm.k_full[sk], (ki / kStagesK) & 1, ctx, kWaitKFull)) return false;
+          KB_FACC(7);
+          tc_fence_after();
+          uint32_t q_lo = desc_lo_kmajor(smem_u32(sm.q[x])), k_lo = desc_lo_kmajor(smem_u32(sm.k[sk]));
+#pragma unroll 1
+          for (int h = 0; h < kPanels; ++h, q_lo += kPanelBytes >> 4, k_lo += kPanelBytes >> 4) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {  // 32 bytes of every row per instruction: 16 16-bit or 32 8-bit elements
+              if (FP8) mma_ss_lo_f8(tmem + kColS + x * 128, q_lo + 2 * i, k_lo + 2 * i, idesc_qk, h > 0 || i > 0);
+              else mma_ss_lo(tmem + kColS + x * 128, q_lo + 2 * i, k_lo + 2 * i, idesc_qk, h > 0 || i > 0);
+            }
+          }
+          if (release_k) mma_commit(&sm.k_empty[sk]);
+          mma_commit(&sm.s_ready[x]);
+          ++tiles_x[x];
+          KB_FACC(8);
+          return true;
+        };
+        if (it.act[0] && it.act[1] && d == 0 && n_x[0] == n_x[1]) {
+          // The usual case, both q tiles on the same key tiles at the same steps (chunks of at least the item's
+          // 256 rows): nothing to work out per step; tile B is the last user of every K and V tile.
+          const int n = n_x[0];
+          for (int step = 0; ok && step <= n; ++step) {
+#pragma unroll
+            for (int x = 0; x < kQTiles; ++x) {
+              if (ok && step >= 1) ok = issue_pv(x, step - 1, kbase + step - 1, x == kQTiles - 1, step == n);
+              if (ok && step < n) ok = issue_s(x, kbase + step, x == kQTiles - 1);
+            }
+            if (step == n - 1) mma_commit(&sm.q_empty);  // every S of this item has been issued
+          }
+        } else {
+          // (the same two issue sequences, written out: through the lambdas this path measured 3-4 % slower)
+          for (int step = 0; ok && step <= n_steps; ++step) {
+  #pragma unroll
+            for (int x = 0; x < kQTiles; ++x) {
+              const bool pv_live = it.act[x] && step - 1 >= first_x[x] && step - 1 < first_x[x] + n_x[x];
+              const bool s_live = it.act[x] && step >= first_x[x] && step < first_x[x] + n_x[x];
+              if (pv_live) {
+                const int lx = step - 1 - first_x[x];  // index within this q tile's range
+                const int u = it.kr[x].begin + lx, vi = kbase + (u - it.u_begin), sv = vi % kStagesV;
+                const int px = tiles_x[x] - 1;  // P block consumed now = last S block issued for x
+                KB_FACC(2);
+                if (!mbar_wait(&sm.p_ready[x], px & 1, ctx, kWaitPReady)) { ok = false; break; }
+                KB_FACC(3 + x);
+                if (!mbar_wait(&sm.v_full[sv], (vi / kStagesV) & 1, ctx, kWaitVFull)) { ok = false; break; }
+                KB_FACC(5);
+                // the first P V of an item overwrites O: the softmax warps must have read the old one
+                if (lx == 0 && items_x[x] > 0 && !mbar_wait(&sm.o_free[x], (items_x[x] - 1) & 1, ctx, kWaitOFree)) { ok = false; break; }
+                tc_fence_after();
+                // short issue loops (four instructions per trip, descriptor low words stepped by adds): the
+                // scalar work between two MMAs is what the tensor pipe waits for
+                uint32_t p_col = tmem + kColS + x * 128, v_lo = desc_lo_mnmajor(smem_u32(sm.v[sv]), kPanelBytes);
+                if (FP8) {
+                  // 128 keys = four instructions of 32 keys: 8 packed columns of P, 32 rows (4096 bytes) of V each
+  #pragma unroll
+                  for (int i = 0; i < 4; ++i)
+                    mma_ts_lo_f8(tmem + kColO + x * 128, p_col + 8 * i, v_lo + i * (4096 >> 4), idesc_pv, lx > 0 || i > 0);
+                } else {
+  #pragma unroll 1
+                  for (int h = 0; h < kBN / 64; ++h, p_col += 32, v_lo += 4 * (2048 >> 4)) {
+  #pragma unroll
+                    for (int i = 0; i < 4; ++i)
+                      mma_ts_lo(tmem + kColO + x * 128, p_col + 8 * i, v_lo + i * (2048 >> 4), idesc_pv, lx > 0 || h > 0 || i > 0);
+                  }
+                }
+                // V_u is free once the last q tile that uses it has consumed it
+                if (last_user(x, u)) mma_commit(&sm.v_empty[sv]);
+                if (u == it.kr[x].end - 1) mma_commit(&sm.o_done[x]);
+                KB_FACC(6);
+              }
+              if (s_live) {
+                const int t = it.kr[x].begin + (step - first_x[x]);
+                const int ki = kbase + (t - it.u_begin), sk = ki % kStagesK;
+                KB_FACC(2);
+                if (!mbar_wait(&sm.k_full[sk], (ki / kStagesK) & 1, ctx, kWaitKFull)) { ok = false; break; }
+                KB_FACC(7);
+                tc_fence_after();
+                uint32_t q_lo = desc_lo_kmajor(smem_u32(sm.q[x])), k_lo = desc_lo_kmajor(smem_u32(sm.k[sk]));
+  #pragma unroll 1
+                for (int h = 0; h < kPanels; ++h, q_lo += kPanelBytes >> 4, k_lo += kPanelBytes >> 4) {
+  #pragma unroll
+                  for (int i = 0; i < 4; ++i) {  // 32 bytes of every row per instruction: 16 16-bit or 32 8-bit elements
+                    if (FP8) mma_ss_lo_f8(tmem + kColS + x * 128, q_lo + 2 * i, k_lo + 2 * i, idesc_qk, h > 0 || i > 0);
+                    else mma_ss_lo(tmem + kColS + x * 128, q_lo + 2 * i, k_lo + 2 * i, idesc_qk, h > 0 || i > 0);
+                  }
+                }
+                if (last_user(x, t)) mma_commit(&sm.k_empty[sk]);
+                mma_commit(&sm.s_ready[x]);
+                ++tiles_x[x];
+                KB_FACC(8);
+              }
+            }
+            if (step == n_steps - 1) mma_commit(&sm.q_empty);  // every S of this item has been issued
+          }
         }
         kbase += it.u_end - it.u_begin;
         ++na;
