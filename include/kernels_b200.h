@@ -316,6 +316,9 @@ KB_API uint64_t kb_sa_bwd_varlen_workspace_bytes(int32_t B, int32_t H, int32_t t
  *
  * kb_out_proj:  y = concat_heads(o) w^T.  o [B, H, T, D] with element strides (unit stride along D), w
  *   [E_out, H D] and y [B, T, E_out] contiguous; E_out a multiple of 256.
+ *
+ * Both launch ONE kernel as thread-block clusters of two CTAs (a pair shares each tcgen05.mma over 256 tokens
+ * x 256 features), as many pairs as the device holds at once.
  */
 typedef struct kb_qkv_proj_params {
   const void* x;
