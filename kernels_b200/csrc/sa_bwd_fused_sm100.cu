@@ -47,6 +47,8 @@
 #include <math.h>
 
 #include "common.cuh"
+#include <type_traits>
+
 #include "sm100_ptx.cuh"
 #include "sm100_host.h"
 #include "tiles.h"
@@ -236,7 +238,12 @@ __device__ __forceinline__ uint8_t* ds_slot(const FusedArgs& a, int b, int row0,
   return a.ds_ws + ((((int64_t)b * a.H + h) * n_ktiles + kt) * a.W + slot) * (int64_t)kDsTileBytes;
 }
 
-template <int D, bool BF16, bool PACKED>  // PACKED: one launch over a packed batch (FusedArgs::cu)
+// PACKED: one launch over a packed batch (FusedArgs::cu).  MID: the MMA thread runs the tiles that neither open nor
+// close their work item through a copy of its issue sequence with those two facts compiled in (the class of long
+// items of fully live tiles: head dim 128, chunks of 128 rows or more; 2-7 % on its main kernel).  The other classes
+// measured 3-12 % SLOWER with the second copy in the kernel (shorter items: the rarely run copy falls out of the
+// instruction cache), so they are built without it.
+template <int D, bool BF16, bool PACKED, bool MID>
 __global__ void __launch_bounds__(kThreads, 1)
 sa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                     const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
@@ -463,17 +470,21 @@ sa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
       int n = 0, g = 0;           // live items, tiles so far
       bool ok = cnt > 0 && issue_s(0, 0, true) && issue_dp(0, 0, true, cnt == 1);
       KB_ACC(11);
-      while (ok) {
-        int cnt_next = 0;
-        for (int t = 0; ok && t < cnt; ++t, ++g) {
-          const bool first = t == 0, last = t == cnt - 1;
+      if constexpr (MID) {
+        int cnt_next = 0, t = 0;
+        // One tile: dV(g), S(g+1), dK(g), dP(g+1).  `mid_c`: the tile neither opens nor closes its item, known at
+        // compile time (no tests of either, constant accumulate flags, no item bookkeeping: every scalar instruction
+        // between two MMAs of this thread is time the chain P -> dV -> S waits).
+        auto tile = [&](auto mid_c, const bool first_rt, const bool last_rt) -> bool {
+          constexpr bool mid = decltype(mid_c)::value;
+          const bool first = mid ? false : first_rt, last = mid ? false : last_rt;
           KB_FTR(1, g, 0);
           KB_ACC(0);  // loop
           // dV(g) += P(g) dO(g)
-          if (!mbar_wait(&sm.p_ready, g & 1, ctx, kWPReady)) { ok = false; break; }
+          if (!mbar_wait(&sm.p_ready, g & 1, ctx, kWPReady)) return false;
           KB_ACC(1);  // wait p_ready
           // the first MMAs of an item overwrite dV / dK: the epilogue warps must have read the old ones
-          if (first && n > 0 && !mbar_wait(&sm.dv_free, (n - 1) & 1, ctx, kWAccFree)) { ok = false; break; }
+          if (first && n > 0 && !mbar_wait(&sm.dv_free, (n - 1) & 1, ctx, kWAccFree)) return false;
           KB_FTR(1, g, 1);
           KB_ACC(2);  // wait dv_free
           tc_fence_after();
@@ -482,19 +493,20 @@ sa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
           if (last) mma_commit(&sm.dv_done);  // the epilogue warps start on dV while dK(last) still runs
           KB_FTR(1, g, 2);
           KB_ACC(3);  // issue dV
-          // S(g+1): of this item, or the first of the next live one
+          // S(g+1): of this item, or the first of the next live one.  (Looking for the next item before the wait for
+          // P instead, off the chain, measured no faster on the short-item classes and 1 % slower on this one.)
           if (last) {
             item += gridDim.x;
             cnt_next = next_live(item);
           }
           const bool more = !last || cnt_next > 0;
-          if (more && !issue_s(last ? n + 1 : n, g + 1, last)) { ok = false; break; }
+          if (more && !issue_s(last ? n + 1 : n, g + 1, last)) return false;
           KB_FTR(1, g, 3);
           KB_ACC(4);  // S(g+1) incl. the look for the next item
           // dK(g) += dS(g) Q(g)
-          if (!mbar_wait(&sm.ds_ready[g & 1], (g >> 1) & 1, ctx, kWDsReady)) { ok = false; break; }
+          if (!mbar_wait(&sm.ds_ready[g & 1], (g >> 1) & 1, ctx, kWDsReady)) return false;
           KB_ACC(5);  // wait ds_ready
-          if (first && n > 0 && !mbar_wait(&sm.dk_free, (n - 1) & 1, ctx, kWAccFree)) { ok = false; break; }
+          if (first && n > 0 && !mbar_wait(&sm.dk_free, (n - 1) & 1, ctx, kWAccFree)) return false;
           KB_ACC(6);  // wait dk_free
           KB_FTR(1, g, 4);
           tc_fence_after();
@@ -504,12 +516,71 @@ sa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
           KB_FTR(1, g, 5);
           KB_ACC(7);  // issue dK
           // dP(g+1)
-          if (more && !issue_dp(last ? n + 1 : n, g + 1, last, last ? cnt_next == 1 : t + 1 == cnt - 1)) { ok = false; break; }
+          if (more && !issue_dp(last ? n + 1 : n, g + 1, last, last ? cnt_next == 1 : t + 1 == cnt - 1)) return false;
           KB_ACC(8);  // dP(g+1)
+          return true;
+        };
+        while (ok) {
+          cnt_next = 0;
+          for (t = 0; ok && t < cnt; ++t, ++g) {
+            const bool first = t == 0, last = t == cnt - 1;
+            if (MID && !first && !last) ok = tile(std::true_type{}, false, false);
+            else ok = tile(std::false_type{}, first, last);
+          }
+          if (!ok || cnt_next == 0) break;
+          cnt = cnt_next;
+          ++n;
         }
-        if (cnt_next == 0) break;
-        cnt = cnt_next;
-        ++n;
+      } else {
+        // (the same sequence written out in the loop: through the lambda above these classes measured 1 % slower)
+        while (ok) {
+          int cnt_next = 0;
+          for (int t = 0; ok && t < cnt; ++t, ++g) {
+            const bool first = t == 0, last = t == cnt - 1;
+            KB_FTR(1, g, 0);
+            KB_ACC(0);  // loop
+            // dV(g) += P(g) dO(g)
+            if (!mbar_wait(&sm.p_ready, g & 1, ctx, kWPReady)) { ok = false; break; }
+            KB_ACC(1);  // wait p_ready
+            // the first MMAs of an item overwrite dV / dK: the epilogue warps must have read the old ones
+            if (first && n > 0 && !mbar_wait(&sm.dv_free, (n - 1) & 1, ctx, kWAccFree)) { ok = false; break; }
+            KB_FTR(1, g, 1);
+            KB_ACC(2);  // wait dv_free
+            tc_fence_after();
+            issue_acc(kColDV, kColS, do_addr, first);
+            mma_commit(&sm.do_empty);
+            if (last) mma_commit(&sm.dv_done);  // the epilogue warps start on dV while dK(last) still runs
+            KB_FTR(1, g, 2);
+            KB_ACC(3);  // issue dV
+            // S(g+1): of this item, or the first of the next live one
+            if (last) {
+              item += gridDim.x;
+              cnt_next = next_live(item);
+            }
+            const bool more = !last || cnt_next > 0;
+            if (more && !issue_s(last ? n + 1 : n, g + 1, last)) { ok = false; break; }
+            KB_FTR(1, g, 3);
+            KB_ACC(4);  // S(g+1) incl. the look for the next item
+            // dK(g) += dS(g) Q(g)
+            if (!mbar_wait(&sm.ds_ready[g & 1], (g >> 1) & 1, ctx, kWDsReady)) { ok = false; break; }
+            KB_ACC(5);  // wait ds_ready
+            if (first && n > 0 && !mbar_wait(&sm.dk_free, (n - 1) & 1, ctx, kWAccFree)) { ok = false; break; }
+            KB_ACC(6);  // wait dk_free
+            KB_FTR(1, g, 4);
+            tc_fence_after();
+            issue_acc(kColDK, kColDP, smem_u32(sm.q[g & 1]), first);
+            mma_commit(&sm.q_empty[g & 1]);
+            if (last) mma_commit(&sm.dk_done);
+            KB_FTR(1, g, 5);
+            KB_ACC(7);  // issue dK
+            // dP(g+1)
+            if (more && !issue_dp(last ? n + 1 : n, g + 1, last, last ? cnt_next == 1 : t + 1 == cnt - 1)) { ok = false; break; }
+            KB_ACC(8);  // dP(g+1)
+          }
+          if (cnt_next == 0) break;
+          cnt = cnt_next;
+          ++n;
+        }
       }
 #ifdef KB_TRACE_FUSED
       if (blockIdx.x == 60)
@@ -1053,11 +1124,14 @@ int launch_fused(const kb_sa_bwd_params& p, int32_t c, int32_t back, cudaStream_
   const int64_t n_items_main = (int64_t)p.B * Hk * n_tiles;
   const unsigned grid_main = (unsigned)(n_items_main < n_sm ? n_items_main : n_sm);
 
-  auto main_kern = sa_bwd_fused_kernel<D, BF16, PACKED>;
+  // the class of long items of fully live tiles gets the main kernel with the second copy of the issue sequence
+  const bool mid = D == 128 && c >= 128;
+  auto main_kern = mid ? sa_bwd_fused_kernel<D, BF16, PACKED, D == 128> : sa_bwd_fused_kernel<D, BF16, PACKED, false>;
   auto dq_kern = sa_bwd_dq_kernel<D, BF16, PACKED>;
   static_assert(sizeof(FusedSmem<D>) <= 232448 && sizeof(DqSmem<D>) <= 232448, "shared memory exceeds the 227 KB a CTA may have");
   static std::atomic<bool> main_opted_in[kMaxDevices], dq_opted_in[kMaxDevices];
-  KB_CUDA_TRY(opt_in_smem_once(main_kern, sizeof(FusedSmem<D>), dev, main_opted_in));
+  static std::atomic<bool> main_mid_opted_in[kMaxDevices];
+  KB_CUDA_TRY(opt_in_smem_once(main_kern, sizeof(FusedSmem<D>), dev, mid ? main_mid_opted_in : main_opted_in));
   KB_CUDA_TRY(opt_in_smem_once(dq_kern, sizeof(DqSmem<D>), dev, dq_opted_in));
 
   DeltaArgs da;
