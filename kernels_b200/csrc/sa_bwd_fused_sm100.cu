@@ -238,11 +238,11 @@ __device__ __forceinline__ uint8_t* ds_slot(const FusedArgs& a, int b, int row0,
   return a.ds_ws + ((((int64_t)b * a.H + h) * n_ktiles + kt) * a.W + slot) * (int64_t)kDsTileBytes;
 }
 
-// PACKED: one launch over a packed batch (FusedArgs::cu).  MID: the MMA thread runs the tiles that neither open nor
-// close their work item through a copy of its issue sequence with those two facts compiled in (the class of long
-// items of fully live tiles: head dim 128, chunks of 128 rows or more; 2-7 % on its main kernel).  The other classes
-// measured 3-12 % SLOWER with the second copy in the kernel (shorter items: the rarely run copy falls out of the
-// instruction cache), so they are built without it.
+// PACKED: one launch over a packed batch (FusedArgs::cu).  MID: the MMA thread runs every tile through a copy of its
+// issue sequence that has "opens its work item" and "closes it" compiled in, four copies in all (the class of long
+// items of fully live tiles: head dim 128, chunks of 128 rows or more; 3-5 % on its main kernel, most of it from the
+// copy for the tiles that do neither).  The other classes measured 3-12 % SLOWER with more than one copy in the
+// kernel (shorter items: the rarely run copies fall out of the instruction cache), so they are built with one.
 template <int D, bool BF16, bool PACKED, bool MID>
 __global__ void __launch_bounds__(kThreads, 1)
 sa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
@@ -472,12 +472,11 @@ sa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
       KB_ACC(11);
       if constexpr (MID) {
         int cnt_next = 0, t = 0;
-        // One tile: dV(g), S(g+1), dK(g), dP(g+1).  `mid_c`: the tile neither opens nor closes its item, known at
-        // compile time (no tests of either, constant accumulate flags, no item bookkeeping: every scalar instruction
-        // between two MMAs of this thread is time the chain P -> dV -> S waits).
-        auto tile = [&](auto mid_c, const bool first_rt, const bool last_rt) -> bool {
-          constexpr bool mid = decltype(mid_c)::value;
-          const bool first = mid ? false : first_rt, last = mid ? false : last_rt;
+        // One tile: dV(g), S(g+1), dK(g), dP(g+1), with whether the tile opens / closes its item known at compile
+        // time (inside an item: no tests of either, constant accumulate flags, no item bookkeeping; every scalar
+        // instruction between two MMAs of this thread is time the chain P -> dV -> S waits).
+        auto tile = [&](auto first_c, auto last_c) -> bool {
+          constexpr bool first = decltype(first_c)::value, last = decltype(last_c)::value;
           KB_FTR(1, g, 0);
           KB_ACC(0);  // loop
           // dV(g) += P(g) dO(g)
@@ -524,8 +523,12 @@ sa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
           cnt_next = 0;
           for (t = 0; ok && t < cnt; ++t, ++g) {
             const bool first = t == 0, last = t == cnt - 1;
-            if (MID && !first && !last) ok = tile(std::true_type{}, false, false);
-            else ok = tile(std::false_type{}, first, last);
+            using Yes = std::true_type;
+            using No = std::false_type;
+            if (!first && !last) ok = tile(No{}, No{});
+            else if (first && !last) ok = tile(Yes{}, No{});
+            else if (!first) ok = tile(No{}, Yes{});
+            else ok = tile(Yes{}, Yes{});
           }
           if (!ok || cnt_next == 0) break;
           cnt = cnt_next;
