@@ -234,7 +234,10 @@ def test_single_evaluation_and_two_pass_backward_agree_bitwise(dtype, D):
     _api()
     torch.manual_seed(11)
     for (B, H, T, c, back, lens) in [(2, 3, 1000, 256, 2, [1000, 517]), (2, 2, 700, 48, 3, [700, 333]),
-                                     (1, 2, 300, 10, 5, [299]), (3, 5, 4096, 128, 4, [4096, 100, 2500])]:
+                                     (1, 2, 300, 10, 5, [299]), (3, 5, 4096, 128, 4, [4096, 100, 2500]),
+                                     # the long-sequence class (chunks of 256, six query tiles per key tile), several
+                                     # work items per CTA: the kernel instances with the specialised issue sequences
+                                     (4, 10, 2048, 256, 2, [2048, 2048, 1500, 2048])]:
         q, k, v, do = (torch.randn(B, H, T, D, device="cuda").to(dtype) for _ in range(4))
         lens_t = torch.tensor(lens, dtype=torch.int32, device="cuda")
         o, lse = torch.ops.alexdremov_streaming_attention.forward(q, k, v, lens_t, c, back, D ** -0.5, False, True,
