@@ -171,6 +171,13 @@ def test_every_head_dim_and_dtype(dtype, D):
     _run_case(2, 2, 130, D, 128, 1, dtype, "tricky", True)
 
 
+@pytest.mark.parametrize("D", [64, 128])
+def test_long_sequence_class_with_several_work_items_per_cta(D):
+    """Chunks of 256 rows, 320 forward and 640 backward work items: more than one per CTA, through the kernel
+    instances whose MMA threads run the specialised issue sequences, against the oracle."""
+    _run_case(2, 40, 1024, D, 256, 2, torch.bfloat16, "random", False)
+
+
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16], ids=str)
 @pytest.mark.parametrize("D", [64, 128])
 def test_rows_whose_last_tile_is_the_only_live_one(dtype, D):
