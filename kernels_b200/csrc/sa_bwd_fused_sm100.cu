@@ -493,7 +493,7 @@ sa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
           KB_FTR(1, g, 2);
           KB_ACC(3);  // issue dV
           // S(g+1): of this item, or the first of the next live one.  (Looking for the next item before the wait for
-          // P instead, off the chain, measured no faster on the short-item classes and 1 % slower on this one.)
+          // P instead, off the chain, as the other classes' loop below does, measured 1 % slower in this one.)
           if (last) {
             item += gridDim.x;
             cnt_next = next_live(item);
@@ -540,6 +540,15 @@ sa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
           int cnt_next = 0;
           for (int t = 0; ok && t < cnt; ++t, ++g) {
             const bool first = t == 0, last = t == cnt - 1;
+            // The look for the next live item (a decode per candidate) is done here, before the wait for P: from
+            // that wait to the issue of S(g+1) the thread is on the kernel's critical chain.
+            if (last) {
+              item += gridDim.x;
+              cnt_next = next_live(item);
+            }
+            const bool more = !last || cnt_next > 0;
+            const int n_next = last ? n + 1 : n;                           // item of tile g + 1
+            const bool dp_last = last ? cnt_next == 1 : t + 1 == cnt - 1;  // tile g + 1 closes its item
             KB_FTR(1, g, 0);
             KB_ACC(0);  // loop
             // dV(g) += P(g) dO(g)
@@ -556,12 +565,7 @@ sa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
             KB_FTR(1, g, 2);
             KB_ACC(3);  // issue dV
             // S(g+1): of this item, or the first of the next live one
-            if (last) {
-              item += gridDim.x;
-              cnt_next = next_live(item);
-            }
-            const bool more = !last || cnt_next > 0;
-            if (more && !issue_s(last ? n + 1 : n, g + 1, last)) { ok = false; break; }
+            if (more && !issue_s(n_next, g + 1, last)) { ok = false; break; }
             KB_FTR(1, g, 3);
             KB_ACC(4);  // S(g+1) incl. the look for the next item
             // dK(g) += dS(g) Q(g)
@@ -577,7 +581,7 @@ sa_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_const
             KB_FTR(1, g, 5);
             KB_ACC(7);  // issue dK
             // dP(g+1)
-            if (more && !issue_dp(last ? n + 1 : n, g + 1, last, last ? cnt_next == 1 : t + 1 == cnt - 1)) { ok = false; break; }
+            if (more && !issue_dp(n_next, g + 1, last, dp_last)) { ok = false; break; }
             KB_ACC(8);  // dP(g+1)
           }
           if (cnt_next == 0) break;
